@@ -1,9 +1,10 @@
 from .base import ConfigError, load_config_json, read_key
 from .llama4 import Llama4Config, RopeScaling
 from .presets import PRESETS, preset
+from .tebivik import TebivikConfig
 from .registry import Architecture, known_architectures, register_architecture, resolve, unregister_architecture
 
 __all__ = [
-    "Architecture", "ConfigError", "Llama4Config", "PRESETS", "RopeScaling", "known_architectures",
+    "Architecture", "ConfigError", "Llama4Config", "PRESETS", "RopeScaling", "TebivikConfig", "known_architectures",
     "load_config_json", "preset", "read_key", "register_architecture", "resolve", "unregister_architecture",
 ]

@@ -50,13 +50,23 @@ def known_architectures() -> list[str]:
 
 def resolve(config_json: Mapping[str, Any]) -> Architecture:
     _ensure_builtin()
-    archs = config_json.get("architectures")
-    if not archs or not isinstance(archs, list):
-        raise ConfigError("config.json: key 'architectures' (a list with the model's class name) is missing")
-    name = archs[0]
+    name = architecture_name(config_json)
     if name not in _ARCHITECTURES:
         raise ConfigError(f"config.json: unknown architecture {name!r}; known: {', '.join(sorted(_ARCHITECTURES))}")
     return _ARCHITECTURES[name]
+
+
+def architecture_name(config_json: Mapping[str, Any]) -> str:
+    """The architecture a config.json names: ``architectures[0]`` (a list, the Hugging Face way) or ``architecture``
+    (one name)."""
+    archs = config_json.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = config_json.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: neither 'architectures' (a list with the model's class name) nor 'architecture' "
+                      "(one name) says which model this is")
 
 
 def _ensure_builtin() -> None:

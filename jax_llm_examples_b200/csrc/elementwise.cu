@@ -8,10 +8,10 @@
 #include "common.cuh"
 #include "expert_sort.cuh"
 
-// x[n, :] = table[ids[n], :]                                     (model.py:1191)
+// x[n, :] = scale * table[ids[n], :]                             (model.py:1191; scale 1 there)
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
-                             int D, int V, int* status) {
+                             int D, int V, float scale, int* status) {
   JLX_TL(TL_EMBED);
   pdl_launch_dependents();
   pdl_wait();
@@ -40,21 +40,21 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
         if (i < D8) {
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
           const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
-          reinterpret_cast<float4*>(out)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-          reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(c.x, c.y, e.x, e.y);
+          reinterpret_cast<float4*>(out)[2 * i] = make_float4(scale * a.x, scale * a.y, scale * b.x, scale * b.y);
+          reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(scale * c.x, scale * c.y, scale * e.x, scale * e.y);
         }
       }
     }
     return;
   }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = to_f32<TW>(row[d]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = scale * to_f32<TW>(row[d]);
 }
 
-JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float* x, int N, int D, int V,
+JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float* x, int N, int D, int V, float scale,
                       int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && V > 0, "embed: bad sizes N=%d D=%d V=%d", N, D, V);
   if (N == 0) return 0;
-  JLX_DISPATCH_DTYPE(table_dtype, TW, { JLX_CUDA(jlx_launch_pdl(embed_kernel<TW>, dim3(N), dim3(256), 0, stream, ids, (const TW*)table, x, D, V, status)); });
+  JLX_DISPATCH_DTYPE(table_dtype, TW, { JLX_CUDA(jlx_launch_pdl(embed_kernel<TW>, dim3(N), dim3(256), 0, stream, ids, (const TW*)table, x, D, V, scale, status)); });
   return 0;
 }
 

@@ -103,7 +103,7 @@ class Engine:
         for r in plan.groups:
             self.manager.add_group(r, self.num_pages)
         dev, dt = self.runtime.device, self.runtime.dtype
-        self.kv = [torch.zeros((self.num_pages, 2, c.num_kv_heads, page_size, c.head_dim), dtype=dt, device=dev)
+        self.kv = [torch.zeros((self.num_pages, c.planes, c.num_kv_heads, page_size, c.head_dim), dtype=dt, device=dev)
                    for c in plan.caches]
         self.states = [torch.zeros((max_slots, *s.shape), dtype=s.dtype, device=dev) for s in plan.states]
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -130,7 +130,7 @@ class Engine:
     def tokens_that_fit(model: DecoderModel, page_size: int = 64, memory_fraction: float = 0.9) -> int:
         """Tokens of cache (whole pages) that fit into this fraction of the device memory now free."""
         elem = 4 if model.runtime.dtype == torch.float32 else 2
-        per_token = sum(2 * c.num_kv_heads * c.head_dim * elem for c in model.plan.caches)
+        per_token = sum(c.planes * c.num_kv_heads * c.head_dim * elem for c in model.plan.caches)
         if per_token == 0:
             raise EngineError("this model keeps no keys and values: give max_tokens")
         free, _ = torch.cuda.mem_get_info(model.runtime.device)

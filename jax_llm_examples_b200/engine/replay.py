@@ -29,7 +29,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to whole pages)")
     ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
-    ap.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time")
     args = ap.parse_args(argv)
 
     print("[trace_run] loading torch and the model ...", file=sys.stderr, flush=True)

@@ -109,11 +109,12 @@ def _contig(*ts: torch.Tensor | None) -> None:
 
 
 # ------------------------------------------------------------------------------ elementwise
-def embed(ids: torch.Tensor, table: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor) -> None:
+def embed(ids: torch.Tensor, table: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """x_out[n] = scale * table[ids[n]] in float32."""
     _contig(ids, table, x_out)
     V, D = table.shape
     _run("elementwise", "jlx_embed", _ptr(ids), _ptr(table), c_int(code(table.dtype)), _ptr(x_out),
-         c_int(ids.numel()), c_int(D), c_int(V), _ptr(status), _stream())
+         c_int(ids.numel()), c_int(D), c_int(V), c_float(scale), _ptr(status), _stream())
 
 
 def _splits(t: torch.Tensor | None, splits: int) -> tuple[int, int]:
@@ -200,6 +201,141 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: 
     sp, stride = _splits(gu, splits)
     _run("elementwise", "jlx_silu_mul", _ptr(gu), c_int(code(gu.dtype)), c_int(sp), c_longlong(stride), _ptr(out),
          c_int(code(out.dtype)), c_int(rows), c_int(F), c_int(int(interleaved)), _stream())
+
+
+# ------------------------------------------------------- grouped norms around a sublayer, biases, short convolution
+ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}  # csrc/group_norm.cu
+
+
+def group_norm(x: torch.Tensor, delta: torch.Tensor | None = None, delta_splits: int = 1, delta_bias: torch.Tensor | None = None,
+               post_weight: torch.Tensor | None = None, post_groups: int = 1, mult: float = 1.0,
+               pre_weight: torch.Tensor | None = None, pre_groups: int = 1, pre_norm: bool = True, eps: float = 1e-6,
+               out: torch.Tensor | None = None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None) -> None:
+    """One pass over each row of the float32 residual x [N, D]:
+    x += mult * post_weight * groupnorm(delta + delta_bias) (``delta``: float32 [N, D] or ``delta_splits`` partials of
+    it; without post_weight the sum is added as it is), then out / out32 = pre_weight * groupnorm(x) (``pre_norm``
+    False: x itself).  groupnorm divides each of ``groups`` equal consecutive parts of a row by
+    sqrt(mean(part^2) + eps).  ``out`` may be a view whose rows are longer than D (its row stride is kept).  With
+    row_index, row n reads source row row_index[n] and x is not written back."""
+    _contig(x, delta, delta_bias, post_weight, pre_weight, out32, row_index)
+    N, D = (row_index.numel() if row_index is not None else x.shape[0]), x.shape[1]
+    if x.dtype != torch.float32 or any(t is not None and t.dtype != torch.float32 for t in (delta, delta_bias, post_weight, pre_weight)):
+        raise KernelError("group_norm: the residual stream, what is added to it and the norm weights must be float32")
+    ld_out = D
+    if out is not None:
+        if out.stride(-1) != 1 or out.shape != (N, D):
+            raise KernelError("group_norm: out must be [N, D] with contiguous rows")
+        ld_out = out.stride(0) if N > 1 else D
+    sp, stride = _splits(delta, delta_splits)
+    _run("group_norm", "jlx_group_norm", _ptr(x), _ptr(delta), c_int(sp), c_longlong(stride), _ptr(delta_bias),
+         _ptr(post_weight), c_int(post_groups), c_float(mult), _ptr(pre_weight), c_int(pre_groups), c_int(int(pre_norm)),
+         c_float(eps), _ptr(out), c_int(code(out.dtype) if out is not None else F32), c_longlong(ld_out), _ptr(out32),
+         _ptr(row_index), c_int(N), c_int(D), _stream())
+
+
+def bias_act(rows: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None, add: torch.Tensor | None = None,
+             activation: str = "none", splits: int = 1) -> None:
+    """out = activation(rows + bias + add).  rows: [N, F] or ``splits`` float32 partials [splits, N, F]; bias: float32
+    [F]; add: float32 [N, F]."""
+    _contig(rows, out, bias, add)
+    N, F = out.shape
+    if any(t is not None and t.dtype != torch.float32 for t in (bias, add)):
+        raise KernelError("bias_act: bias and addend must be float32")
+    sp, stride = _splits(rows, splits)
+    _run("group_norm", "jlx_bias_act", _ptr(rows), c_int(code(rows.dtype)), c_int(sp), c_longlong(stride), _ptr(bias), _ptr(add),
+         c_int(ACTIVATIONS[activation]), _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(F), _stream())
+
+
+def short_conv(h32: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, cu_q: torch.Tensor, q_start: torch.Tensor,
+               slot_ids: torch.Tensor, req_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = h[t] + sum_j weight[:, j] * h[t - taps + 1 + j] along each request's time axis (zeros before its start).
+    h32: float32 [N, D]; weight: float32 [D, taps]; state: float32 [slots, taps - 1, D], a request's last inputs,
+    read for the tokens before this step's and moved on."""
+    _contig(h32, weight, state, out)
+    N, D = h32.shape
+    taps = weight.shape[1]
+    if h32.dtype != torch.float32 or weight.dtype != torch.float32 or (state is not None and state.dtype != torch.float32):
+        raise KernelError("short_conv: input, weight and state must be float32")
+    if weight.shape[0] != D or (state is not None and tuple(state.shape[1:]) != (taps - 1, D)):
+        raise KernelError(f"short_conv: shapes do not fit: h {tuple(h32.shape)}, weight {tuple(weight.shape)}")
+    _run("group_norm", "jlx_short_conv", _ptr(h32), _ptr(weight), _ptr(state), _ptr(cu_q), _ptr(q_start), _ptr(slot_ids),
+         _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(slot_ids.numel()), c_int(D),
+         c_int(taps), _stream())
+
+
+# ------------------------------------------------------------------------------- recurrences
+def hgrn2_scan(qfv: torch.Tensor, splits: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, out: torch.Tensor,
+               heads: int, dk: int, dv: int) -> None:
+    """The gated recurrence S = diag(f) S + (1 - f) v^T, o = S^T silu(q) over each request's tokens, with the per-head
+    RMS norm of o.  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their activations (or ``splits`` partials);
+    state: float32 [slots, H, dk, dv]; out: [N, H dv]."""
+    _contig(qfv, f_bias, lower, state, norm_weight, out)
+    if any(t.dtype != torch.float32 for t in (qfv, f_bias, lower, state)) or (norm_weight is not None and norm_weight.dtype != torch.float32):
+        raise KernelError("hgrn2_scan: projections, gate constants, state and norm weight must be float32")
+    if tuple(state.shape[1:]) != (heads, dk, dv) or out.shape[1] != heads * dv:
+        raise KernelError(f"hgrn2_scan: shapes do not fit: state {tuple(state.shape)}, out {tuple(out.shape)}")
+    sp, stride = _splits(qfv, splits)
+    _run("recurrent", "jlx_hgrn2_scan", _ptr(qfv), c_int(sp), c_longlong(stride), _ptr(f_bias), _ptr(lower), _ptr(state),
+         _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(out), c_int(code(out.dtype)),
+         c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), _stream())
+
+
+# -------------------------------------------------------------------------- latent attention
+def latent_kv_prep(proj: torch.Tensor, splits: int, q_norm_weight: torch.Tensor, kv_norm_weight: torch.Tensor, eps: float,
+                   inv_freq: torch.Tensor, rot_dims: int, cq: torch.Tensor, pages: torch.Tensor | None,
+                   block_table: torch.Tensor | None, req_of_token: torch.Tensor, positions: torch.Tensor,
+                   q_rank: int, rank: int, dr: int, status: torch.Tensor) -> None:
+    """From projected rows [N, q_rank + rank + dr] (float32, or partials): cq = weighted RMS norm of the first q_rank
+    entries; the page row of the token = [weighted RMS norm of the next rank entries | the last dr entries, rotated].
+    pages: [P, 1, 1, page_size, rank + dr]."""
+    _contig(proj, q_norm_weight, kv_norm_weight, inv_freq, cq, pages, block_table)
+    N = cq.shape[0]
+    store = pages is not None
+    if store and (pages.dtype != cq.dtype or pages.shape[1:3] != (1, 1) or pages.shape[4] != rank + dr):
+        raise KernelError(f"latent_kv_prep: pages {tuple(pages.shape)} do not fit a latent of {rank} + {dr}")
+    sp, stride = _splits(proj, splits)
+    _run("attention_latent", "jlx_latent_kv_prep", _ptr(proj), c_int(sp), c_longlong(stride), _ptr(q_norm_weight),
+         _ptr(kv_norm_weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims), _ptr(cq), _ptr(pages), c_int(code(cq.dtype)),
+         _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token), _ptr(positions), c_int(N),
+         c_int(q_rank), c_int(rank), c_int(dr), c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0),
+         _ptr(status), _stream())
+
+
+def latent_q_prep(q: torch.Tensor, splits: int, inv_freq: torch.Tensor, rot_dims: int, positions: torch.Tensor,
+                  q_nope: torch.Tensor, q_rot: torch.Tensor, heads: int, dn: int, dr: int) -> None:
+    """q: float32 [N, H (dn + dr)] (or partials) -> q_nope [H, N, dn] (head-major) and q_rot float32 [N, H, dr], rotated."""
+    _contig(q, inv_freq, q_nope, q_rot)
+    N = q_rot.shape[0]
+    sp, stride = _splits(q, splits)
+    _run("attention_latent", "jlx_latent_q_prep", _ptr(q), c_int(sp), c_longlong(stride), _ptr(inv_freq), c_int(rot_dims),
+         _ptr(positions), _ptr(q_nope), c_int(code(q_nope.dtype)), _ptr(q_rot), c_int(N), c_int(heads), c_int(dn), c_int(dr),
+         _stream())
+
+
+def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     req_of_token: torch.Tensor, positions: torch.Tensor, sink: torch.Tensor | None, out_lat: torch.Tensor,
+                     scale: float, status: torch.Tensor) -> None:
+    """Causal attention in the latent space with an optional per-head sink.  q_lat: float32 [H, N, rank]; q_rot:
+    float32 [N, H, dr]; pages: [P, 1, 1, page_size, rank + dr]; out_lat: [H, N, rank]."""
+    _contig(q_lat, q_rot, pages, block_table, sink, out_lat)
+    H, N, rank = q_lat.shape
+    dr = q_rot.shape[2]
+    if q_lat.dtype != torch.float32 or q_rot.dtype != torch.float32 or (sink is not None and sink.dtype != torch.float32):
+        raise KernelError("attention_latent: queries and sinks must be float32")
+    if pages.shape[4] != rank + dr:
+        raise KernelError("attention_latent: cache rows and queries disagree in size")
+    _run("attention_latent", "jlx_attention_latent", _ptr(q_lat), _ptr(q_rot), _ptr(pages), c_int(code(pages.dtype)),
+         _ptr(block_table), c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), _ptr(sink), _ptr(out_lat),
+         c_int(code(out_lat.dtype)), c_int(N), c_int(H), c_int(rank), c_int(dr), c_int(pages.shape[3]), c_int(pages.shape[0]),
+         c_float(scale), _ptr(status), _stream())
+
+
+def heads_to_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """x: [H, N, d] -> out: [N, H * d]."""
+    _contig(x, out)
+    H, N, d = x.shape
+    _run("attention_latent", "jlx_heads_to_rows", _ptr(x), _ptr(out), c_int(code(x.dtype)), c_int(N), c_int(H), c_int(d), _stream())
 
 
 # ------------------------------------------------------------------- position encoding + cache

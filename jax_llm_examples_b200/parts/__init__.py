@@ -1,14 +1,19 @@
 from .attention import PagedAttention, plan_attention_tiles
-from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, Rows, RowSum, Runtime, StateNeed,
+from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, PostNormed, Rows, RowSum, Runtime, StateNeed,
                    StepContext, StepShape, Workspace, as_rows, known_parts, make_part, register_part)
-from .block import PreNormBlock
+from .block import PreNormBlock, ReinjectionBlock, SandwichNormBlock
+from .conv import ResidualShortConv
 from .decoder import CachePlan, DecoderModel, LayerRun
-from .feedforward import DenseSwiGLU, RoutedExperts
+from .feedforward import DenseBiasedMLP, DenseSwiGLU, RoutedExperts
+from .latent_attention import LatentAttention, rotary_frequencies
 from .linear import grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
-from .norms import RMSNorm
+from .norms import GroupRMSNorm, RMSNorm, add_to_residual
+from .recurrent import HGRN2, InputConvMixer
 from .positions import InterleavedRope, NoPositionWithTemperature, UnfusedEncoding, llama3_scaled_frequencies
 
 __all__ = [
+    "DenseBiasedMLP", "GroupRMSNorm", "HGRN2", "InputConvMixer", "LatentAttention", "PostNormed", "ReinjectionBlock",
+    "ResidualShortConv", "SandwichNormBlock", "add_to_residual", "rotary_frequencies",
     "Block", "CachePlan", "DecoderModel", "DenseSwiGLU", "FeedForward", "InterleavedRope", "KVNeed", "LayerCache",
     "LayerRun", "Mixer", "NoPositionWithTemperature", "Norm", "PagedAttention", "Part", "PositionEncoding",
     "PreNormBlock", "RMSNorm", "RoutedExperts", "Rows", "RowSum", "Runtime", "Workspace", "as_rows", "grouped_swiglu_linear", "interleave_gate_up", "swiglu_linear", "StateNeed", "StepContext", "StepShape", "plan_attention_tiles", "UnfusedEncoding",

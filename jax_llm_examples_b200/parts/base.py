@@ -41,11 +41,13 @@ class Runtime:
 
 @dataclasses.dataclass(frozen=True)
 class KVNeed:
-    """Pages of keys and values: heads, head size, and which keys stay readable."""
+    """Pages of keys and values: heads, head size, and which keys stay readable.  ``planes``: 2 = a key and a value
+    row per token and head; 1 = one row (a mixer that keeps a latent from which it makes both)."""
 
     num_kv_heads: int
     head_dim: int
     retention: Retention
+    planes: int = 2
 
 
 @dataclasses.dataclass(frozen=True)
@@ -81,10 +83,33 @@ class RowSum:
     materialize: Callable[[], torch.Tensor]
 
 
-def as_rows(x: "torch.Tensor | Rows | RowSum | None") -> "Rows | None":
+@dataclasses.dataclass
+class PostNormed:
+    """A delta that is still to be normed before it is added: x += mult * weight * groupnorm(rows + bias), the
+    closing norm of a block that norms a sublayer's output as well as its input.  A norm that can (``GroupRMSNorm``)
+    does this in the same pass over the row as the residual sum and its own norm; ``materialize()`` makes the plain
+    [N, D] float32 tensor for a consumer that cannot: :func:`as_rows` calls it."""
+
+    rows: Rows
+    weight: torch.Tensor  # float32 [D]
+    eps: float
+    groups: int
+    mult: float
+    bias: torch.Tensor | None = None  # float32 [D], added to the rows before the norm (a biased product's bias)
+
+    def materialize(self) -> torch.Tensor:
+        from ..kernels import api as K
+
+        n, d = self.rows.data.shape[-2], self.rows.data.shape[-1]
+        zero = torch.zeros((n, d), dtype=torch.float32, device=self.weight.device)
+        K.group_norm(zero, self.rows.data, self.rows.splits, self.bias, self.weight, self.groups, self.mult, eps=self.eps)
+        return zero
+
+
+def as_rows(x: "torch.Tensor | Rows | RowSum | PostNormed | None") -> "Rows | None":
     if x is None or isinstance(x, Rows):
         return x
-    if isinstance(x, RowSum):
+    if isinstance(x, (RowSum, PostNormed)):
         return Rows(x.materialize(), 1)
     return Rows(x, 1)
 
@@ -135,7 +160,8 @@ class LayerCache:
     pages: torch.Tensor | None  # [num_pages, 2, Hkv, page_size, dh]
     block_table: torch.Tensor | None  # int32 [R, width], rows in the order of the step's requests
     writes: bool  # False: the layer reads a cache that another layer fills
-    state: torch.Tensor | None  # [max_slots, *StateNeed.shape]
+    state: torch.Tensor | None  # [max_slots, *StateNeed.shape]; the first slab of a mixer that has several
+    states: tuple = ()  # all slabs of the run, in the order of the mixer's ``state_needs()``
 
 
 @dataclasses.dataclass
@@ -277,11 +303,19 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    needs_f32_input: bool = False  # True: forward() gets the normed rows unrounded (``h32=``) and no rounded ones
+
     def kv_need(self) -> KVNeed | None:
         return None
 
     def state_need(self) -> StateNeed | None:
         return None
+
+    def state_needs(self) -> "tuple[StateNeed, ...]":
+        """Every per-request state of the mixer (one slab each, ``cache.states`` in this order): a recurrence's
+        state beside the last inputs of a short convolution, say.  The default is the single ``state_need()``."""
+        one = self.state_need()
+        return () if one is None else (one,)
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> "torch.Tensor | Rows":
         """h: normed rows [N, D] in the runtime's dtype.  Returns delta [N, D] float32 (or Rows of partials)."""
@@ -302,7 +336,7 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    mixer: Mixer
+    mixer: "Mixer | None"  # None: a block that mixes nothing across tokens and keeps no cache or state
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: "torch.Tensor | Rows | None", cache: LayerCache):
         """Runs the block on residual x with a pending ``delta`` not yet added; returns the new pending delta."""
@@ -311,7 +345,7 @@ class Block(Part):
 
 # ------------------------------------------------------------------------------ part registry
 _PARTS: dict[tuple[str, str], Callable[..., Part]] = {}
-KINDS = ("norm", "position", "mixer", "feed_forward", "block")
+KINDS = ("norm", "position", "mixer", "feed_forward", "block", "conv")
 
 
 def register_part(kind: str, name: str, factory: Callable[..., Part]) -> None:

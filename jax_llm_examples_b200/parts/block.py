@@ -34,3 +34,97 @@ class PreNormBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class SandwichNormBlock(Block):
+    """A block that norms each sublayer's input and its output, and scales what it adds:
+
+        x += mult * norm1b(mixer(norm1(x)));   x += mult * norm2b(feed_forward(norm2(x)))
+
+    ``feed_forward`` (with its two norms) may be None: the block then has the first sublayer only.
+    A sublayer's output goes on as a :class:`PostNormed` delta: the closing norm, the scaled residual sum and the
+    next opening norm are one kernel.  ``feed_forward.bias_out`` (the bias of its last product), if it has one, is
+    added inside that kernel too."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm1b: Norm, norm2: Norm | None = None,
+                 feed_forward: FeedForward | None = None, norm2b: Norm | None = None, mult: float = 1.0):
+        if (feed_forward is None) != (norm2 is None) or (feed_forward is None) != (norm2b is None):
+            raise ValueError("a feed-forward comes with both of its norms, or not at all")
+        self.norm1, self.mixer, self.norm1b = norm1, mixer, norm1b
+        self.norm2, self.feed_forward, self.norm2b = norm2, feed_forward, norm2b
+        self.mult = float(mult)
+
+    def sub_parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.feed_forward, self.norm2b) if p is not None)
+
+    def _closing(self, norm: Norm, y, bias=None):
+        from .base import PostNormed, as_rows
+
+        return PostNormed(as_rows(y), norm.weight, norm.eps, norm.groups, self.mult, bias)
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache):
+        dt = ctx.runtime.dtype
+        with scope("attn_pre_norm"):
+            if self.mixer.needs_f32_input:
+                _, h32, _ = self.norm1.forward(ctx, x, delta, out_dtype=None, want_f32=True)
+                y = self.mixer.forward(ctx, None, cache, h32=h32)
+            else:
+                h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
+                y = self.mixer.forward(ctx, h, cache)
+        pending = self._closing(self.norm1b, y)
+        if self.feed_forward is None:
+            return pending
+        with scope("attn_post_norm"):
+            h = self.norm2.forward(ctx, x, pending, out_dtype=dt)[0]
+        with scope("ffn"):
+            y = self.feed_forward.forward(ctx, h, None, None)
+        return self._closing(self.norm2b, y, getattr(self.feed_forward, "bias_out", None))
+
+
+class ReinjectionBlock(Block):
+    """Feeds the embedding's output into the stream again:  x <- W [x; x0] + step,  x0 = what the embedding put out
+    for the token, W: [D, 2D] (x's half first), ``step``: a vector of this entry (one per pass of a loop over layers).
+    It mixes nothing across tokens and keeps no cache or state.  The product of W's second half with x0 is the same
+    for every such block of a step that shares W: it is made once and kept in the step's scratch."""
+
+    mixer = None
+    wants_embedding_output = True
+    kernel_libraries = ("group_norm",)
+
+    def __init__(self, w_in: torch.Tensor, step: torch.Tensor):
+        D = w_in.shape[0]
+        if w_in.shape[1] != 2 * D or step.shape != (D,):
+            raise ValueError(f"re-injection weights do not fit: {tuple(w_in.shape)}, step {tuple(step.shape)}")
+        self.w_x, self.w_x0 = w_in[:, :D].contiguous(), w_in[:, D:].contiguous()
+        self.step = step.to(torch.float32).contiguous()
+
+    def share_weights(self, other: "ReinjectionBlock") -> None:
+        """Another pass over the same W: keep one copy of its halves."""
+        self.w_x, self.w_x0 = other.w_x, other.w_x0
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache):
+        from ..kernels import api as K
+        from .base import as_rows
+        from .linear import linear
+        from .norms import add_to_residual
+
+        dt = ctx.runtime.dtype
+        n, D = x.shape
+        key = ("reinjection", self.w_x0.data_ptr())
+        u0 = ctx.scratch.get(key)
+        if u0 is None:
+            x0 = torch.empty((n, D), dtype=dt, device=x.device)
+            K.bias_act(ctx.scratch["embedding_output"], x0)
+            u = as_rows(linear(ctx, x0, self.w_x0, torch.float32, partials=True))
+            u0 = torch.empty((n, D), dtype=torch.float32, device=x.device)
+            K.bias_act(u.data, u0, splits=u.splits)
+            ctx.scratch[key] = u0
+        xa = torch.empty((n, D), dtype=dt, device=x.device)
+        add_to_residual(x, delta, pre_norm=False, out=xa)  # x += pending; xa = x in the activations' type
+        y = as_rows(linear(ctx, xa, self.w_x, torch.float32, partials=True))
+        K.bias_act(y.data, x, self.step, u0, splits=y.splits)  # x = W_x x + W_x0 x0 + step
+        return None
+
+
+register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("block", "reinjection", ReinjectionBlock)

@@ -22,7 +22,11 @@ class LayerRun:
     block: int  # index into the model's blocks
     cache: int | None = None  # index of the cache it reads (None: the mixer keeps no keys and values)
     writes: bool = True  # False: another run fills that cache
-    state: int | None = None  # index of its per-request state slab (None: stateless)
+    state: "int | tuple[int, ...] | None" = None  # its per-request state slab(s) (None: stateless)
+
+    @property
+    def state_indices(self) -> tuple:
+        return () if self.state is None else ((self.state,) if isinstance(self.state, int) else tuple(self.state))
 
 
 @dataclasses.dataclass(frozen=True)
@@ -37,19 +41,33 @@ class DecoderModel:
     """Embedding, scheduled blocks, final norm, LM head (llama4/llama4_jax/model.py:1186-1204)."""
 
     def __init__(self, runtime: Runtime, embedding: torch.Tensor, blocks: list[Block], final_norm: Norm,
-                 lm_head: torch.Tensor, schedule: list[LayerRun] | None = None, config=None):
+                 lm_head: torch.Tensor, schedule: list[LayerRun] | None = None, config=None, embedding_scale: float = 1.0):
         self.runtime, self.embedding, self.blocks = runtime, embedding, blocks
         self.final_norm, self.lm_head, self.config = final_norm, lm_head, config
+        self.embedding_scale = float(embedding_scale)  # the residual stream starts as scale * embedding row
         self.vocab_size, self.hidden_size = embedding.shape
         if schedule is None:
-            schedule, c, s = [], 0, 0
-            for i, b in enumerate(blocks):
-                has_kv, has_state = b.mixer.kv_need() is not None, b.mixer.state_need() is not None
-                schedule.append(LayerRun(i, c if has_kv else None, True, s if has_state else None))
-                c += has_kv
-                s += has_state
+            schedule = self.schedule_of([(i,) for i in range(len(blocks))], blocks)
         self.schedule = list(schedule)
         self.plan = self._make_plan()
+        # a block that wants the embedding's output later on (to feed it in again) gets a copy of it in
+        # ``ctx.scratch["embedding_output"]``
+        self.keeps_embedding_output = any(getattr(b, "wants_embedding_output", False) for b in blocks)
+
+    @staticmethod
+    def schedule_of(order, blocks: list[Block]) -> list[LayerRun]:
+        """The schedule that runs ``blocks[i]`` for every ``(i, ...)`` of ``order`` in turn, every run with a cache
+        and state slabs of its own (a block named twice shares its weights between runs, nothing else)."""
+        schedule, c, s = [], 0, 0
+        for i, *_ in order:
+            mixer = blocks[i].mixer
+            has_kv = mixer is not None and mixer.kv_need() is not None
+            n_state = 0 if mixer is None else len(mixer.state_needs())
+            state = None if n_state == 0 else (s if n_state == 1 else tuple(range(s, s + n_state)))
+            schedule.append(LayerRun(i, c if has_kv else None, True, state))
+            c += has_kv
+            s += n_state
+        return schedule
 
     def _make_plan(self) -> CachePlan:
         caches: dict[int, KVNeed] = {}
@@ -57,6 +75,10 @@ class DecoderModel:
         states: dict[int, StateNeed] = {}
         for pos, run in enumerate(self.schedule):
             mixer = self.blocks[run.block].mixer
+            if mixer is None:
+                if run.cache is not None or run.state is not None:
+                    raise ValueError(f"schedule entry {pos}: a block without a mixer has no cache and no state")
+                continue
             need = mixer.kv_need()
             if (need is None) != (run.cache is None):
                 raise ValueError(f"schedule entry {pos}: the block's mixer {'needs' if need else 'has'} no cache index")
@@ -70,19 +92,19 @@ class DecoderModel:
                     if run.cache not in writers:
                         raise ValueError(f"schedule entry {pos}: reads cache {run.cache} before any entry fills it")
                     w = caches[run.cache]
-                    if (w.num_kv_heads, w.head_dim) != (need.num_kv_heads, need.head_dim):
+                    if (w.num_kv_heads, w.head_dim, w.planes) != (need.num_kv_heads, need.head_dim, need.planes):
                         raise ValueError(f"schedule entry {pos}: cache {run.cache} has other head sizes than this mixer")
                     if w.retention != need.retention:
                         # the reader must not need keys that the writer's group gives back
                         if w.retention != Retention.all():
                             raise ValueError(f"schedule entry {pos}: reads a cache whose pages are released by another rule")
-            sn = mixer.state_need()
-            if (sn is None) != (run.state is None):
+            needs = mixer.state_needs()
+            if len(needs) != len(run.state_indices):
                 raise ValueError(f"schedule entry {pos}: state index does not match the mixer's need")
-            if sn is not None:
-                if run.state in states:
-                    raise ValueError(f"schedule entry {pos}: state {run.state} is used twice")
-                states[run.state] = sn
+            for idx, sn in zip(run.state_indices, needs):
+                if idx in states:
+                    raise ValueError(f"schedule entry {pos}: state {idx} is used twice")
+                states[idx] = sn
         if sorted(caches) != list(range(len(caches))) or sorted(states) != list(range(len(states))):
             raise ValueError("cache and state indices must be 0..n-1 without gaps")
         groups: list[Retention] = []
@@ -140,14 +162,17 @@ class DecoderModel:
         """Runs the step's tokens through the schedule; returns float32 logits [M, V] at ctx.logit_rows."""
         rt = self.runtime
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=rt.device)
-        K.embed(ctx.token_ids, self.embedding, x, ctx.status)
+        K.embed(ctx.token_ids, self.embedding, x, ctx.status, self.embedding_scale)
+        if self.keeps_embedding_output:
+            ctx.scratch["embedding_output"] = x.clone()
         delta = None
         for run in self.schedule:
+            slabs = tuple(states[i] for i in run.state_indices)
+            first = slabs[0] if slabs else None
             if run.cache is None:
-                cache = LayerCache(None, None, False, None if run.state is None else states[run.state])
+                cache = LayerCache(None, None, False, first, slabs)
             else:
-                cache = LayerCache(kv[run.cache], block_tables[self.plan.group_of[run.cache]], run.writes,
-                                   None if run.state is None else states[run.state])
+                cache = LayerCache(kv[run.cache], block_tables[self.plan.group_of[run.cache]], run.writes, first, slabs)
             delta = self.blocks[run.block].forward(ctx, x, delta, cache)
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=rt.device)

@@ -198,3 +198,35 @@ class RoutedExperts(FeedForward):
 
 register_part("feed_forward", "dense_swiglu", DenseSwiGLU)
 register_part("feed_forward", "routed_experts", RoutedExperts)
+
+
+class DenseBiasedMLP(FeedForward):
+    """down(act(h up + b_up)) + b_down with a pointwise activation (``relu2``: the square of relu; ``silu``;
+    ``gelu_tanh``; ``none``).  ``w_up``: [F, D]; ``w_down``: [D, F].  The first bias and the activation run in one
+    kernel on the product's (partial) sums.  The last bias is not added here: ``bias_out`` offers it to whoever adds
+    this part's output to the residual stream (a block whose closing norm takes it into its own kernel); a block
+    that knows nothing of it must add it itself."""
+
+    kernel_libraries = ("group_norm", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
+
+    def __init__(self, w_up: torch.Tensor, b_up: torch.Tensor | None, w_down: torch.Tensor, b_down: torch.Tensor | None,
+                 activation: str = "relu2"):
+        if w_up.shape[0] != w_down.shape[1] or w_up.shape[1] != w_down.shape[0]:
+            raise ValueError(f"MLP weights do not fit: up {tuple(w_up.shape)}, down {tuple(w_down.shape)}")
+        if activation not in K.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(K.ACTIVATIONS)}")
+        self.w_up, self.w_down, self.activation = w_up, w_down, activation
+        self.b_up = None if b_up is None else b_up.to(torch.float32).contiguous()
+        self.bias_out = None if b_down is None else b_down.to(torch.float32).contiguous()
+
+    def forward(self, ctx: StepContext, h, h32=None, routing=None):
+        with scope("gate_up_proj"):
+            up = as_rows(linear(ctx, h, self.w_up, torch.float32, partials=True))
+            act = torch.empty((h.shape[0], self.w_up.shape[0]), dtype=ctx.runtime.dtype, device=h.device)
+            K.bias_act(up.data, act, self.b_up, None, self.activation, up.splits)
+        with scope("down_proj"):
+            return linear(ctx, act, self.w_down, torch.float32, partials=True)
+
+
+register_part("feed_forward", "dense_biased", DenseBiasedMLP)

@@ -1,0 +1,121 @@
+"""Attention over one cached latent per token, from which every head's keys and values are made."""
+
+from __future__ import annotations
+
+import functools
+
+import numpy as np
+import torch
+
+from ..cache.manager import Retention
+from ..kernels import api as K
+from ..tracing import scope
+from .base import KVNeed, LayerCache, StepContext, StepShape, as_rows, register_part
+from .conv import ResidualShortConv
+from .linear import grouped_linear, linear
+from .recurrent import InputConvMixer
+
+
+def rotary_frequencies(base: float, dims: int) -> torch.Tensor:
+    """f_i = base^(-2i / dims), i < dims / 2, evaluated in float64 and rounded once to float32."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return (float(base) ** (-2.0 * i / dims)).to(torch.float32)
+
+
+@functools.lru_cache(maxsize=None)
+def plan_head_groups(heads: int):
+    """The step planner for per-head products over head-major rows [H, N, ...]: the row offsets h * N of the heads'
+    groups (one planner per head count; mixers with the same count share it)."""
+    name = f"head_group_offsets_{heads}"
+
+    def planner(shape: StepShape) -> dict[str, np.ndarray]:
+        n = int(sum(shape.q_lens))
+        return {name: np.arange(heads + 1, dtype=np.int32) * n}
+
+    planner.array_name = name
+    return planner
+
+
+class LatentAttention(InputConvMixer):
+    """Causal attention with low-rank queries and ONE cached latent per token.
+
+    c_q = RMSnorm(W_dq h) * w_qn;  q = W_uq c_q, per head [dn unrotated | dr rotated].
+    W_dkv h = [c_pre (rank) | k_rot (dr)];  c = RMSnorm(c_pre) * w_kvn;  k_rot is rotated and shared by all heads.
+    Per head: k_nope = W_uk c, v = W_uv c;  score = (q_nope . k_nope + q_rot . k_rot) * scale;  the softmax's
+    denominator also holds exp(sink_h) (no key, no value);  out = W_o [heads' weighted values].
+
+    Only [c | k_rot] is cached (``planes`` = 1, one "head" of rank + dr).  The kernels work in the latent space:
+    q_lat = W_uk[h]^T q_nope (a product per head), scores and weighted sums against the cached rows, then
+    v = W_uv[h] out_lat (a product per head).  Rotation: the first ``rot_dims`` entries of the rotated part, in pairs
+    (2i, 2i+1), by position * rot_base^(-2i / rot_dims).
+
+    ``w_down``: [q_rank + rank + dr, D] = W_dq over W_dkv.  ``w_uk``: [H dn, rank]; ``w_uv``: [H dv, rank]."""
+
+    kernel_libraries = ("attention_latent", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
+
+    def __init__(self, w_down: torch.Tensor, q_norm_weight: torch.Tensor, w_uq: torch.Tensor, kv_norm_weight: torch.Tensor,
+                 w_uk: torch.Tensor, w_uv: torch.Tensor, w_o: torch.Tensor, sink: torch.Tensor | None, heads: int, dim: int,
+                 rot_dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float, rot_base: float, rot_dims: int, eps: float,
+                 input_conv: ResidualShortConv | None = None):
+        H, dn, dr, dv = heads, dim, rot_dim, vdim
+        ok = (w_down.shape[0] == q_rank + kv_rank + dr and tuple(w_uq.shape) == (H * (dn + dr), q_rank)
+              and tuple(w_uk.shape) == (H * dn, kv_rank) and tuple(w_uv.shape) == (H * dv, kv_rank)
+              and w_o.shape[1] == H * dv and q_norm_weight.numel() == q_rank and kv_norm_weight.numel() == kv_rank
+              and (sink is None or sink.numel() == H))
+        if not ok:
+            raise ValueError(f"latent attention weights do not fit {H} heads of {dn}+{dr}/{dv}, ranks {q_rank}/{kv_rank}")
+        if rot_dims % 2 or not 0 <= rot_dims <= dr:
+            raise ValueError(f"{rot_dims} rotated entries of a rotated part of {dr}")
+        self.w_down, self.w_uq, self.w_o = w_down, w_uq, w_o
+        self.q_norm_weight = q_norm_weight.to(torch.float32).contiguous()
+        self.kv_norm_weight = kv_norm_weight.to(torch.float32).contiguous()
+        # per head: q_lat = W_uk[h]^T q_nope needs [rank, dn] as the product's [out, in]; v = W_uv[h] out_lat has it already
+        self.w_uk_t = w_uk.reshape(H, dn, kv_rank).transpose(1, 2).contiguous()
+        self.w_uv = w_uv.reshape(H, dv, kv_rank).contiguous()
+        self.sink = None if sink is None else sink.to(torch.float32).contiguous()
+        self.heads, self.dim, self.rot_dim, self.vdim = H, dn, dr, dv
+        self.q_rank, self.kv_rank, self.scale, self.eps = q_rank, kv_rank, float(scale), float(eps)
+        self.rot_dims = rot_dims
+        self.inv_freq = rotary_frequencies(rot_base, rot_dims).to(w_down.device) if rot_dims else \
+            torch.zeros(1, dtype=torch.float32, device=w_down.device)
+        self.input_conv = input_conv
+        self._planner = plan_head_groups(H)
+
+    def kv_need(self) -> KVNeed:
+        return KVNeed(1, self.kv_rank + self.rot_dim, Retention.all(), planes=1)
+
+    def step_planners(self):
+        return (self._planner,)
+
+    def forward(self, ctx: StepContext, h, cache: LayerCache, h32: torch.Tensor | None = None):
+        dt, dev = ctx.runtime.dtype, h32.device
+        a, _ = self.read_input(ctx, h32, cache)
+        n, H = a.shape[0], self.heads
+        offsets = ctx.arrays[self._planner.array_name]
+        with scope("qkv_matmul"):
+            down = as_rows(linear(ctx, a, self.w_down, torch.float32, partials=True))
+        cq = torch.empty((n, self.q_rank), dtype=dt, device=dev)
+        with scope("rope"):  # both latents' norms, the shared key part's rotation and the page write in one kernel
+            K.latent_kv_prep(down.data, down.splits, self.q_norm_weight, self.kv_norm_weight, self.eps, self.inv_freq,
+                             self.rot_dims, cq, cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
+                             ctx.req_of_token, ctx.positions, self.q_rank, self.kv_rank, self.rot_dim, ctx.status)
+        with scope("qkv_matmul"):
+            q = as_rows(linear(ctx, cq, self.w_uq, torch.float32, partials=True))
+        q_nope = torch.empty((H, n, self.dim), dtype=dt, device=dev)
+        q_rot = torch.empty((n, H, self.rot_dim), dtype=torch.float32, device=dev)
+        with scope("rope"):
+            K.latent_q_prep(q.data, q.splits, self.inv_freq, self.rot_dims, ctx.positions, q_nope, q_rot, H, self.dim, self.rot_dim)
+        with scope("attention"):
+            q_lat = grouped_linear(ctx, q_nope.view(H * n, self.dim), self.w_uk_t, offsets, torch.float32, largest_group=n)
+            out_lat = torch.empty((H, n, self.kv_rank), dtype=dt, device=dev)
+            K.attention_latent(q_lat.view(H, n, self.kv_rank), q_rot, cache.pages, cache.block_table, ctx.req_of_token,
+                               ctx.positions, self.sink, out_lat, self.scale, ctx.status)
+            v = grouped_linear(ctx, out_lat.view(H * n, self.kv_rank), self.w_uv, offsets, dt, largest_group=n)
+            rows = torch.empty((n, H * self.vdim), dtype=dt, device=dev)
+            K.heads_to_rows(v.view(H, n, self.vdim), rows)
+        with scope("projection"):
+            return linear(ctx, rows, self.w_o, torch.float32, partials=True)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

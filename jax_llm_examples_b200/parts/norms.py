@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .base import Norm, RowSum, StepContext, as_rows, register_part
+from .base import Norm, Rows, RowSum, StepContext, as_rows, register_part
 
 
 class RMSNorm(Norm):
@@ -63,3 +63,52 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rms", RMSNorm)
+
+
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: a row is cut into ``groups`` equal consecutive parts, each part is divided by its own
+    sqrt(mean(part^2) + eps), and the whole is multiplied by ``weight`` (``groups`` = 1 is the plain RMS norm).
+
+    The pending delta may be a :class:`PostNormed`: a sublayer's output that is itself to be group-normed, scaled
+    and then added.  That norm, the residual sum and this norm run in one pass over the row (one kernel)."""
+
+    kernel_libraries = ("group_norm",)
+
+    def __init__(self, weight: torch.Tensor, eps: float, groups: int = 1):
+        if weight.numel() % groups:
+            raise ValueError(f"{groups} norm groups do not divide the width {weight.numel()}")
+        self.weight = weight.to(torch.float32).contiguous()
+        self.eps, self.groups = float(eps), int(groups)
+
+    def forward(self, ctx: StepContext, x, delta, *, out_dtype, want_f32=False, row_index=None, router=None):
+        """``out_dtype`` None: only the float32 rows are made (for a consumer that takes those)."""
+        n = x.shape[0] if row_index is None else row_index.numel()
+        out = None if out_dtype is None else torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
+        out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=x.device) if want_f32 else None
+        add_to_residual(x, delta, pre_weight=self.weight, pre_groups=self.groups, eps=self.eps, out=out, out32=out32,
+                        row_index=row_index)
+        return out, out32, None
+
+
+def add_to_residual(x: torch.Tensor, delta, *, pre_weight=None, pre_groups: int = 1, pre_norm: bool = True, eps: float = 1e-6,
+                    out=None, out32=None, row_index=None) -> None:
+    """x += delta, whatever form the pending delta has (None, a tensor, split-K partials, a :class:`PostNormed`),
+    and, in the same pass, out / out32 = the group norm of the new x (``pre_norm`` False: the new x itself)."""
+    from .base import PostNormed
+
+    if isinstance(delta, PostNormed):
+        if abs(delta.eps - eps) > 0:
+            # one kernel takes one eps: norm the delta on its own first
+            delta = Rows(delta.materialize(), 1)
+        else:
+            K.group_norm(x, delta.rows.data, delta.rows.splits, delta.bias, delta.weight, delta.groups, delta.mult,
+                         pre_weight, pre_groups, pre_norm, eps, out, out32, row_index)
+            return
+    d = as_rows(delta)
+    if d is not None and d.data.dtype != torch.float32:
+        d = Rows(d.data.to(torch.float32), d.splits)
+    K.group_norm(x, None if d is None else d.data, 1 if d is None else d.splits, None, None, 1, 1.0,
+                 pre_weight, pre_groups, pre_norm, eps, out, out32, row_index)
+
+
+register_part("norm", "group_rms", GroupRMSNorm)

@@ -27,7 +27,7 @@ import torch
 class TensorSpec:
     name: str
     shape: tuple[int, ...]
-    init: str = "normal"  # "normal": N(0, std);  "norm": 1 + N(0, norm_noise)
+    init: str = "normal"  # "normal": N(0, std); "norm": 1 + N(0, norm_noise); "bias": N(0, 1/4); "unit": in (0, 1)
     optional: bool = False
 
 

@@ -36,6 +36,10 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device: str |
         t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
         if spec.init == "norm":
             return (1.0 + norm_noise * t).to(dtype)
+        if spec.init == "unit":  # a value in (0, 1): lower bounds of gates and the like
+            return torch.sigmoid(t).to(dtype)
+        if spec.init == "bias":  # biases, per-channel filters, sinks: wide enough to matter
+            return (0.5 * t).to(dtype)
         return (std * t).to(dtype)
     # large tensors: draw in the target precision, slab by slab, to bound the temporary
     out = torch.empty(spec.shape, dtype=dtype, device=device)

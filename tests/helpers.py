@@ -160,12 +160,13 @@ def trace_mixed(requests, rng: random.Random, max_live=4, portions=SHORT_PORTION
     return steps
 
 
-def run_trace(engine, steps):
+def run_trace(engine, steps, record_routing: bool = True):
     """Drives the engine's step function with a trace.  Returns (logits by (request, position),
-    expert choices by (request, position): one array [k] per routed layer, in layer order)."""
+    expert choices by (request, position): one array [k] per routed layer, in layer order).
+    ``record_routing`` False: nothing is recorded, so decode steps may be replayed from CUDA graphs."""
     from jax_llm_examples_b200 import StepEntry
 
-    engine.record_routing = True
+    engine.record_routing = record_routing
     slots: dict[str, int] = {}
     at: dict[str, int] = {}
     out: dict[tuple[str, int], np.ndarray] = {}
