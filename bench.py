@@ -468,6 +468,119 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": f"the reference was imported but did not run: {type(e).__name__}: {str(e)[:300]}"}
 
 
+def run_compare(args) -> dict:
+    """--compare tebivik: prefill and decode throughput of Tebivik at layer sizes of real models beside the closest
+    model the framework had before (a dense Llama-4-style decoder of the same width, depth and head count), random
+    weights, one GPU; with each model's device time by kernel for one prompt step and one decode step, and for the
+    kernels that differ between the two the fraction of the measured roofline that they reach."""
+    import torch
+
+    import jax_llm_examples_b200 as J
+    from jax_llm_examples_b200 import tracing
+    from jax_llm_examples_b200.config.presets import dense_llama_sized, tebivik_sized
+
+    peaks, peak_src = _peaks()
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    torch.cuda.set_device(0)
+    P, B, C = args.prefill_tokens, args.batch, min(args.context, 4096)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sizes = [(2048, 8, 16, 8192), (4096, 8, 32, 14336)]
+    if args.layers:
+        sizes = [(w, args.layers, h, f) for w, _, h, f in sizes]
+    out = {"metric": "prefill and decode throughput, Tebivik beside a dense Llama-4-style decoder", "unit": "tok/s", "n_gpus": 1,
+           "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": peaks, "peaks_source": peak_src,
+           "config": {"prefill_tokens": P, "decode_batch": B, "decode_context": C, "l2": "a 256 MiB buffer is written between timed steps"},
+           "sizes": []}
+
+    def measure(cfg_json):
+        model = J.random_model(cfg_json, seed=0, dtype="bfloat16")
+        vocab = model.vocab_size
+        eng = J.Engine(model, max_tokens=B * (C + 64), page_size=64, max_slots=B + 1)
+        rng = __import__("random").Random(0)
+        prompt = lambda n: [rng.randrange(vocab) for _ in range(n)]
+
+        def timed(fn, steps, warmup):
+            for _ in range(warmup):
+                fn()
+            ms = []
+            for _ in range(steps):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms.append(e0.elapsed_time(e1))
+            return sorted(ms)[len(ms) // 2]
+
+        def one_prefill():
+            s = eng.new_request()
+            eng.step([J.StepEntry(s, prompt(P), [P - 1])])
+            eng.finish(s)
+
+        prefill_ms = timed(one_prefill, 5, 3)
+        kt = tracing.KernelTimer()
+        with kt:
+            one_prefill()
+        prefill_kernels = {k: round(v[1], 4) for k, v in kt.by_kernel.items()}
+        slots = [eng.new_request() for _ in range(B)]
+        for s in slots:  # fill the cache: the requests' first C - 40 tokens
+            eng.step([J.StepEntry(s, prompt(C - 40), [])])
+
+        def one_decode():
+            eng.step([J.StepEntry(s, prompt(1), [0]) for s in slots])
+
+        decode_ms = timed(one_decode, 20, 4)
+        kt = tracing.KernelTimer()
+        with kt:
+            for _ in range(4):
+                one_decode()
+        decode_kernels = {k: round(v[1] / 4, 4) for k, v in kt.by_kernel.items()}
+        eng.check_status()
+        res = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(P / prefill_ms * 1e3), "prefill_ms": round(prefill_ms, 3),
+               "decode_tok_s": round(B / decode_ms * 1e3), "decode_ms": round(decode_ms, 4), "graph_replays": eng.graph_replays,
+               "prefill_kernels_ms": prefill_kernels, "decode_kernels_ms": decode_kernels}
+        del eng, model
+        torch.cuda.empty_cache()
+        return res
+
+    def frac(ms, nbytes=0.0, flops=0.0):
+        """Fraction of the roofline: the time the bytes need at the measured copy rate, or the FLOPs at the measured
+        bf16 rate (whichever is longer), over the measured time."""
+        return round(max(nbytes / hbm, flops / tflops) / (ms * 1e-3), 4) if ms else None
+
+    clocks = ClockSampler()
+    clocks.start()
+    for width, layers, heads, ff in sizes:
+        t_cfg, l_cfg = tebivik_sized(width, layers, heads, ff), dense_llama_sized(width, layers, heads, ff)
+        t, l = measure(t_cfg), measure(l_cfg)
+        runs = layers + layers // 2  # the first half of Tebivik's layers runs twice
+        att_runs = sum(1 for i in range(layers) if i % 2 == 0) + sum(1 for i in range(layers // 2) if i % 2 == 0)
+        rec_runs = runs - att_runs
+        rank, dr, dh, hkv = 512, 64, 128, max(heads // 4, 1)
+        roof = {
+            "decode": {
+                "tebivik attention_latent": frac(t["decode_kernels_ms"].get("jlx_attention_latent", 0), att_runs * B * C * (rank + dr) * 2),
+                "tebivik hgrn2_scan": frac(t["decode_kernels_ms"].get("jlx_hgrn2_scan", 0), rec_runs * B * heads * 128 * 128 * 8),
+                "tebivik group_norm": frac(t["decode_kernels_ms"].get("jlx_group_norm", 0), (2 * runs + 1) * B * width * 14),
+                "llama attention_decode": frac(l["decode_kernels_ms"].get("jlx_attention_decode", 0), layers * B * C * 2 * hkv * dh * 2),
+                "llama add_rmsnorm": frac(l["decode_kernels_ms"].get("jlx_add_rmsnorm", 0), (2 * layers + 1) * B * width * 14),
+            },
+            "prefill": {
+                "tebivik attention_latent": frac(t["prefill_kernels_ms"].get("jlx_attention_latent", 0), 0, att_runs * heads * P * P / 2 * 2 * (2 * rank + dr)),
+                "tebivik hgrn2_scan": frac(t["prefill_kernels_ms"].get("jlx_hgrn2_scan", 0), rec_runs * P * (2 * heads * 128 + heads * 128) * 4, 0),
+                "tebivik group_norm": frac(t["prefill_kernels_ms"].get("jlx_group_norm", 0), (2 * runs + 1) * P * width * 14),
+                "llama attention_prefill_tc": frac(l["prefill_kernels_ms"].get("jlx_attention_prefill_tc", 0), 0, layers * heads * P * P / 2 * 4 * dh),
+                "llama add_rmsnorm": frac(l["prefill_kernels_ms"].get("jlx_add_rmsnorm", 0), (2 * layers + 1) * P * width * 14),
+            },
+        }
+        out["sizes"].append({"width": width, "layers": layers, "layer_runs_tebivik": runs, "heads": heads, "ff": ff, "tebivik": t,
+                             "dense_llama": l, "fraction_of_measured_roofline": roof})
+    out["clocks"] = clocks.stop()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -486,7 +599,13 @@ def main() -> int:
     ap.add_argument("--long-tokens", type=int, default=32768)
     ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
+    ap.add_argument("--compare", default=None, choices=["tebivik"],
+                    help="instead of the benchmark: throughput of this architecture at real layer sizes beside the closest "
+                    "model the framework had before (with --prefill-tokens, --batch, --context up to 4096, --layers)")
     args = ap.parse_args()
+    if args.compare:
+        print(json.dumps(run_compare(args)))
+        return 0
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0

@@ -54,6 +54,48 @@ PRESETS: dict[str, dict[str, Any]] = {
         use_qk_norm=False, attention_chunk_size=8192, no_rope_layers=[1, 1, 1, 0], attn_temperature_tuning=True,
         floor_scale=8192.0, attn_scale=0.1, rms_norm_eps=1e-5, tie_word_embeddings=False),
 }
+
+
+def tebivik_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 32768) -> dict[str, Any]:
+    """A Tebivik configuration at the layer sizes of a real model: latent attention (head size 128 + 64 rotated, latent
+    512, query latent 3/8 of the width) and HGRN2 (state 128 x 128 per head) in turn, a feed-forward in every layer,
+    the first half of the layers run twice."""
+    att = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": 512,
+                     "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}},
+           "mlp": {"kind": "dense", "ff": ff}}
+    rec = {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Tebivik", "vocab": vocab, "width": width, "residual_mult": 0.7, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "loop": {"start": 0, "stop": layers // 2, "times": 2},
+            "layers": [att if i % 2 == 0 else rec for i in range(layers)]}
+
+
+def dense_llama_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 32768) -> dict[str, Any]:
+    """The closest model the framework had before: a dense Llama-4-style decoder of the same width, depth, head count
+    and head size (4 query heads per KV head, SwiGLU of two thirds the other's feed-forward width, so that the
+    feed-forward weights weigh the same), every layer rotary and unchunked."""
+    return _text(num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=max(heads // 4, 1),
+                 head_dim=128, interleave_moe_layer_step=0, moe_layers=[], num_local_experts=1, num_experts_per_tok=1,
+                 intermediate_size=ff * 2 // 3 // 64 * 64, intermediate_size_mlp=ff * 2 // 3 // 64 * 64, vocab_size=vocab,
+                 rope_theta=10000.0, rope_scaling=None, use_qk_norm=False, attention_chunk_size=1 << 20,
+                 no_rope_layers=[1] * layers, attn_temperature_tuning=False, floor_scale=8192.0, attn_scale=0.1,
+                 rms_norm_eps=1e-6, tie_word_embeddings=True)
+
+
+# Tebivik: a tiny one (every size a multiple of 8, so bfloat16 products run on the tensor cores) and real layer sizes.
+PRESETS["tebivik_tiny"] = {
+    "architecture": "Tebivik", "vocab": 256, "width": 64, "residual_mult": 0.5, "embedding": {"scale": 2.0},
+    "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 3}, "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        {"type": "hgrn2", "mixer": {"heads": 2, "dim": 16, "vdim": 24}, "mlp": {"kind": "dense", "ff": 96}},
+        {"type": "latent_attention", "mlp": None,
+         "mixer": {"heads": 4, "dim": 16, "rot_dim": 8, "vdim": 16, "q_rank": 24, "kv_rank": 32, "scale": 0.2,
+                   "rot": {"base": 10000.0, "dims": 8}}},
+        {"type": "hgrn2", "mixer": {"heads": 4, "dim": 8, "vdim": 16}, "mlp": None},
+    ],
+}
+PRESETS["tebivik_2k"] = tebivik_sized(2048, 8, 16, 8192)
+PRESETS["tebivik_4k"] = tebivik_sized(4096, 8, 32, 14336)
 PRESETS["scout8_long"] = {**PRESETS["scout16"], "num_hidden_layers": 8, "no_rope_layers": _every_nth_nope(8, 4)}
 
 
@@ -62,7 +104,7 @@ def preset(name: str, **overrides: Any) -> dict[str, Any]:
         raise KeyError(f"unknown preset {name!r}; known: {', '.join(sorted(PRESETS))}")
     d = dict(PRESETS[name])
     d.update(overrides)
-    if "num_hidden_layers" in overrides and "no_rope_layers" not in overrides:
+    if "num_hidden_layers" in overrides and "no_rope_layers" not in overrides and "no_rope_layers" in PRESETS[name]:
         n = overrides["num_hidden_layers"]
         base = PRESETS[name]["no_rope_layers"]
         d["no_rope_layers"] = [base[i % len(base)] for i in range(n)]

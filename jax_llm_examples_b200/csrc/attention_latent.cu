@@ -90,16 +90,22 @@ JLX_API int jlx_latent_kv_prep(const float* proj, int splits, long long split_st
   return 0;
 }
 
-// q: float32 [N, H, dn + dr] (or partials).  q_nope: [H, N, dn] in the activation type; q_rot: float32 [N, H, dr].
+// q: float32 [N, H, dn + dr] (or partials).  q_nope: [H, N, dn] in the activation type; q_rot: float32 [N, H, dr];
+// q_full (optional): [H, N, dn + dr] in the activation type, the rotated part rotated (for per-head score products).
 template <typename TO>
 __global__ void latent_q_prep_kernel(const float* __restrict__ q, int splits, long long split_stride,
                                      const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
-                                     TO* __restrict__ q_nope, float* __restrict__ q_rot, int N, int H, int dn, int dr) {
+                                     TO* __restrict__ q_nope, float* __restrict__ q_rot, TO* __restrict__ q_full, int N, int H,
+                                     int dn, int dr) {
   JLX_TL(TL_ROPE);
   const int n = blockIdx.x, h = blockIdx.y;
   const float* row = q + ((size_t)n * H + h) * (dn + dr);
-  for (int i = threadIdx.x; i < dn; i += blockDim.x)
-    q_nope[((size_t)h * N + n) * dn + i] = from_f32<TO>(row_sum_splits(row + i, splits, split_stride));
+  TO* full = q_full ? q_full + ((size_t)h * N + n) * (dn + dr) : nullptr;
+  for (int i = threadIdx.x; i < dn; i += blockDim.x) {
+    const TO v = from_f32<TO>(row_sum_splits(row + i, splits, split_stride));
+    q_nope[((size_t)h * N + n) * dn + i] = v;
+    if (full) full[i] = v;
+  }
   const float* qr = row + dn;
   float* dst = q_rot + ((size_t)n * H + h) * dr;
   const int p = positions[n];
@@ -107,22 +113,28 @@ __global__ void latent_q_prep_kernel(const float* __restrict__ q, int splits, lo
     float sn, cs;
     sincosf((float)p * inv_freq[i], &sn, &cs);
     const float u = row_sum_splits(qr + 2 * i, splits, split_stride), v = row_sum_splits(qr + 2 * i + 1, splits, split_stride);
-    dst[2 * i] = u * cs - v * sn;
-    dst[2 * i + 1] = v * cs + u * sn;
+    const float a = u * cs - v * sn, b = v * cs + u * sn;
+    dst[2 * i] = a;
+    dst[2 * i + 1] = b;
+    if (full) { full[dn + 2 * i] = from_f32<TO>(a); full[dn + 2 * i + 1] = from_f32<TO>(b); }
   }
-  for (int i = rot_dims + threadIdx.x; i < dr; i += blockDim.x) dst[i] = row_sum_splits(qr + i, splits, split_stride);
+  for (int i = rot_dims + threadIdx.x; i < dr; i += blockDim.x) {
+    const float v = row_sum_splits(qr + i, splits, split_stride);
+    dst[i] = v;
+    if (full) full[dn + i] = from_f32<TO>(v);
+  }
 }
 
 JLX_API int jlx_latent_q_prep(const float* q, int splits, long long split_stride, const float* inv_freq, int rot_dims,
-                              const int* positions, void* q_nope, int dtype, float* q_rot, int N, int H, int dn, int dr,
-                              cudaStream_t stream) {
+                              const int* positions, void* q_nope, int dtype, float* q_rot, void* q_full, int N, int H, int dn,
+                              int dr, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && H > 0 && dn > 0 && dr >= 0 && splits >= 1, "latent_q_prep: bad sizes");
   JLX_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0, "latent_q_prep: %d rotated entries of %d", rot_dims, dr);
   JLX_REQUIRE(H <= 65535, "latent_q_prep: too many heads (%d)", H);
   if (N == 0) return 0;
   JLX_DISPATCH_DTYPE(dtype, TO, {
     latent_q_prep_kernel<TO><<<dim3(N, H), 64, 0, stream>>>(q, splits, split_stride, inv_freq, rot_dims, positions, (TO*)q_nope,
-                                                            q_rot, N, H, dn, dr);
+                                                            q_rot, (TO*)q_full, N, H, dn, dr);
   });
   JLX_LAUNCH_CHECK("latent_q_prep");
   return 0;
@@ -136,54 +148,93 @@ JLX_API int jlx_latent_q_prep(const float* q, int splits, long long split_stride
 #define LAT_WARPS 8
 #define LAT_MAX_R32 32  // latent size up to 1024
 
+// With `rows` the block serves token rows[blockIdx.x] (the single decoded tokens of a step that also holds prompt
+// portions).  With splits > 1 block z takes the keys [z * split_keys, (z + 1) * split_keys) (a multiple of the tile, so
+// tiles stay aligned) and leaves (m, l, unnormalised sums) for the combine kernel; the sink opens split 0.
 template <typename TC, typename TO>
 __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot,
                                         const TC* __restrict__ pages, const int* __restrict__ block_table, int bt_stride,
                                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                         const float* __restrict__ sink, TO* __restrict__ out_lat, int N, int H, int rank,
-                                        int dr, int page_size, int num_pages, float scale, int* status) {
+                                        int dr, int page_size, int num_pages, float scale, const int* __restrict__ rows,
+                                        int splits, int split_keys, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                                        int* status) {
   JLX_TL(TL_ATTN_GENERIC);
   extern __shared__ float smem[];
   const int dk = rank + dr, ldk = dk + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __shared__ long long row_at[LAT_TILE];  // row number of each key of the tile in the pool, -1: a bad page
   float* qs = smem;               // [nwarp][dk]
   float* ks = qs + nwarp * dk;    // [LAT_TILE][dk + 1]
-  const int n = blockIdx.x;
+  const int n = rows ? rows[blockIdx.x] : blockIdx.x;
   const int h = blockIdx.y * nwarp + warp;
+  const int z = blockIdx.z;
   const bool active = h < H;
   const int p = positions[n], r = req_of_token[n];
   if (active) {
     for (int d = lane; d < rank; d += 32) qs[warp * dk + d] = q_lat[((size_t)h * N + n) * rank + d];
     for (int d = lane; d < dr; d += 32) qs[warp * dk + rank + d] = q_rot[((size_t)n * H + h) * dr + d];
   }
-  const bool has_sink = sink != nullptr;
+  const bool has_sink = sink != nullptr && z == 0;
   float m = (active && has_sink) ? sink[h] : -INFINITY, l = has_sink ? 1.f : 0.f;
   float acc[LAT_MAX_R32];
 #pragma unroll
   for (int i = 0; i < LAT_MAX_R32; ++i) acc[i] = 0.f;
   const int nd = (rank + 31) >> 5;
+  const int t_begin = splits > 1 ? z * split_keys : 0;
+  const int t_end = splits > 1 ? min(p, (z + 1) * split_keys - 1) : p;  // last key of this block
 
-  for (int t0 = 0; t0 <= p; t0 += LAT_TILE) {
+  // 16-byte loads of the cached rows where their size and the pool's address allow
+  constexpr int VEC = 16 / (int)sizeof(TC);
+  const bool wide = (dk % VEC) == 0 && ((uintptr_t)pages & 15) == 0;
+  bool bad_page = false;
+  for (int t0 = t_begin; t0 <= t_end; t0 += LAT_TILE) {
     __syncthreads();  // the previous tile is consumed; qs is visible
-    const int cnt = min(LAT_TILE, p - t0 + 1);
-    for (int idx = threadIdx.x; idx < cnt * dk; idx += blockDim.x) {
-      const int j = idx / dk, d = idx - j * dk;
-      const int pos = t0 + j;
-      const int page = block_table[(size_t)r * bt_stride + pos / page_size];
-      float kv = 0.f;
-      if (page < 0 || page >= num_pages) atomicOr(status, JLX_STATUS_BAD_PAGE);
-      else kv = to_f32<TC>(pages[((size_t)page * page_size + pos % page_size) * dk + d]);
-      ks[j * ldk + d] = kv;
+    const int cnt = min(LAT_TILE, t_end - t0 + 1);
+    if (threadIdx.x < cnt) {  // where the tile's rows lie
+      const int pos = t0 + threadIdx.x;
+      int page = block_table[(size_t)r * bt_stride + pos / page_size];
+      if (page < 0 || page >= num_pages) { bad_page = true; page = -1; }
+      row_at[threadIdx.x] = page < 0 ? -1 : (long long)page * page_size + pos % page_size;
+    }
+    __syncthreads();
+    if (wide) {
+      const int chunks = dk / VEC;
+#pragma unroll 4
+      for (int idx = threadIdx.x; idx < cnt * chunks; idx += blockDim.x) {
+        const int j = idx / chunks, ch = idx - j * chunks;
+        const long long at = row_at[j];
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (at >= 0) raw = *reinterpret_cast<const uint4*>(pages + (size_t)at * dk + ch * VEC);
+        const TC* e = reinterpret_cast<const TC*>(&raw);
+        float* dst = ks + j * ldk + ch * VEC;
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) dst[u] = to_f32<TC>(e[u]);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < cnt * dk; idx += blockDim.x) {
+        const int j = idx / dk, d = idx - j * dk;
+        const long long at = row_at[j];
+        ks[j * ldk + d] = at >= 0 ? to_f32<TC>(pages[(size_t)at * dk + d]) : 0.f;
+      }
     }
     __syncthreads();
     if (active) {
       float s = -INFINITY;
       if (lane < cnt) {
-        float dot = 0.f;
+        // four running sums (in a fixed order), so that the products do not wait for one another
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
         const float* kr = ks + lane * ldk;
         const float* qr = qs + warp * dk;
-        for (int d = 0; d < dk; ++d) dot = fmaf(qr[d], kr[d], dot);
-        s = dot * scale;
+        int d = 0;
+        for (; d + 3 < dk; d += 4) {
+          d0 = fmaf(qr[d], kr[d], d0);
+          d1 = fmaf(qr[d + 1], kr[d + 1], d1);
+          d2 = fmaf(qr[d + 2], kr[d + 2], d2);
+          d3 = fmaf(qr[d + 3], kr[d + 3], d3);
+        }
+        for (; d < dk; ++d) d0 = fmaf(qr[d], kr[d], d0);
+        s = ((d0 + d1) + (d2 + d3)) * scale;
       }
       const float m_new = fmaxf(m, warp_max(s));
       const float corr = expf(m - m_new);  // without a sink m is -inf on the first tile: exp(-inf) = 0
@@ -191,49 +242,185 @@ __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const f
       l = l * corr + warp_sum(pj);
       m = m_new;
 #pragma unroll
-      for (int i = 0; i < LAT_MAX_R32; ++i) {
-        if (i < nd) {
-          const int d = lane + 32 * i;
-          float a = acc[i] * corr;
-          for (int j = 0; j < cnt; ++j) {
-            const float pv = __shfl_sync(0xffffffffu, pj, j);
-            if (d < rank) a = fmaf(pv, ks[j * ldk + d], a);
-          }
-          acc[i] = a;
-        }
+      for (int i = 0; i < LAT_MAX_R32; ++i) acc[i] *= corr;
+      for (int j = 0; j < cnt; ++j) {  // key by key: the lane's entries of the latent are independent sums
+        const float pv = __shfl_sync(0xffffffffu, pj, j);
+        const float* kj = ks + j * ldk + lane;
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_R32; ++i)
+          if (i < nd && lane + 32 * i < rank) acc[i] = fmaf(pv, kj[32 * i], acc[i]);
       }
     }
   }
-  if (active) {
+  if (bad_page) atomicOr(status, JLX_STATUS_BAD_PAGE);
+  if (!active) return;
+  if (splits > 1) {
+    const size_t slot = ((size_t)blockIdx.x * H + h) * splits + z;
+    if (lane == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
 #pragma unroll
     for (int i = 0; i < LAT_MAX_R32; ++i) {
       const int d = lane + 32 * i;
-      if (i < nd && d < rank) out_lat[((size_t)h * N + n) * rank + d] = from_f32<TO>(acc[i] / l);
+      if (i < nd && d < rank) part_acc[slot * rank + d] = acc[i];
     }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < LAT_MAX_R32; ++i) {
+    const int d = lane + 32 * i;
+    if (i < nd && d < rank) out_lat[((size_t)h * N + n) * rank + d] = from_f32<TO>(acc[i] / l);
   }
 }
 
+// out = sum_z acc_z exp(m_z - m) / sum_z l_z exp(m_z - m), m = max_z m_z, the splits in ascending order.
+template <typename TO>
+__global__ void attention_latent_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                TO* __restrict__ out_lat, const int* __restrict__ rows, int N, int H, int rank,
+                                                int splits) {
+  JLX_TL(TL_ATTN_COMBINE);
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int n = rows ? rows[b] : b;
+  const size_t slot0 = ((size_t)b * H + h) * splits;
+  float m = -INFINITY;
+  for (int z = 0; z < splits; ++z) m = fmaxf(m, part_ml[2 * (slot0 + z)]);
+  float l = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = part_ml[2 * (slot0 + z)];
+    if (mz > -INFINITY) l += part_ml[2 * (slot0 + z) + 1] * expf(mz - m);
+  }
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float a = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = part_ml[2 * (slot0 + z)];
+      if (mz > -INFINITY) a = fmaf(part_acc[(slot0 + z) * rank + d], expf(mz - m), a);
+    }
+    out_lat[((size_t)h * N + n) * rank + d] = from_f32<TO>(a / l);
+  }
+}
+
+// rows / n_rows: serve these token rows only (N stays the row count of q and out).  splits > 1: part_acc float32
+// [n_rows * H * splits * rank], part_ml float32 [n_rows * H * splits * 2].
 JLX_API int jlx_attention_latent(const float* q_lat, const float* q_rot, const void* pages, int cache_dtype,
                                  const int* block_table, int bt_stride, const int* req_of_token, const int* positions,
                                  const float* sink, void* out_lat, int out_dtype, int N, int H, int rank, int dr,
-                                 int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
+                                 int page_size, int num_pages, float scale, const int* rows, int n_rows, int splits,
+                                 int split_keys, float* part_acc, float* part_ml, int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && H > 0 && rank > 0 && dr >= 0 && page_size > 0 && num_pages > 0, "attention_latent: bad sizes");
   JLX_REQUIRE(rank <= 32 * LAT_MAX_R32, "attention_latent: latent size %d is above the supported maximum %d", rank, 32 * LAT_MAX_R32);
-  if (N == 0) return 0;
+  JLX_REQUIRE(splits >= 1 && splits <= 65535, "attention_latent: bad split count %d", splits);
+  JLX_REQUIRE(splits == 1 || (split_keys > 0 && split_keys % LAT_TILE == 0 && part_acc && part_ml),
+              "attention_latent: splits need a key count that is a multiple of %d, and scratch", LAT_TILE);
+  const int served = rows ? n_rows : N;
+  if (served == 0) return 0;
   const int nwarp = H < LAT_WARPS ? H : LAT_WARPS;
   const int dk = rank + dr;
   const size_t smem = sizeof(float) * ((size_t)nwarp * dk + (size_t)LAT_TILE * (dk + 1));
   JLX_REQUIRE(smem <= 200 * 1024, "attention_latent: a key tile of %d x %d does not fit into shared memory", LAT_TILE, dk);
   const int hb = (H + nwarp - 1) / nwarp;
-  JLX_REQUIRE(hb <= 65535, "attention_latent: too many heads (%d)", H);
+  JLX_REQUIRE(hb <= 65535 && H <= 65535, "attention_latent: too many heads (%d)", H);
   JLX_DISPATCH_DTYPE(cache_dtype, TC, JLX_DISPATCH_DTYPE(out_dtype, TO, {
     if (smem > 48 * 1024)
       JLX_CUDA(cudaFuncSetAttribute(attention_latent_kernel<TC, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attention_latent_kernel<TC, TO><<<dim3(N, hb), nwarp * 32, smem, stream>>>(
+    attention_latent_kernel<TC, TO><<<dim3(served, hb, splits), nwarp * 32, smem, stream>>>(
         q_lat, q_rot, (const TC*)pages, block_table, bt_stride, req_of_token, positions, sink, (TO*)out_lat, N, H, rank, dr,
-        page_size, num_pages, scale, status);
+        page_size, num_pages, scale, rows, splits, split_keys, part_acc, part_ml, status);
   }));
   JLX_LAUNCH_CHECK("attention_latent");
+  if (splits > 1) {
+    JLX_DISPATCH_DTYPE(out_dtype, TO, {
+      attention_latent_combine_kernel<TO><<<dim3(served, H), 128, 0, stream>>>(part_acc, part_ml, (TO*)out_lat, rows, N, H, rank, splits);
+    });
+    JLX_LAUNCH_CHECK("attention_latent_combine");
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ prompt portions
+// For a prompt portion the scores and the weighted sums are per-head matrix products on the tensor cores (the caller's,
+// from the library), around three kernels of this file: the request's cached rows gathered into two dense matrices,
+// the keys put together per head, and the softmax with its causal edge and its sink.
+
+// c[t, :] = cache row t's first `rank` entries, kr[t, :] = its last dr, t < L, for the request of block-table row r.
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pages, const int* __restrict__ bt_row, T* __restrict__ c,
+                                     T* __restrict__ kr, int rank, int dr, int page_size, int num_pages, int* status) {
+  JLX_TL(TL_OTHER);
+  const int t = blockIdx.x;
+  const int page = bt_row[t / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, JLX_STATUS_BAD_PAGE);
+    return;
+  }
+  const T* src = pages + ((size_t)page * page_size + t % page_size) * (rank + dr);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) c[(size_t)t * rank + i] = src[i];
+  for (int i = threadIdx.x; i < dr; i += blockDim.x) kr[(size_t)t * dr + i] = src[rank + i];
+}
+
+JLX_API int jlx_latent_gather(const void* pages, int dtype, const int* bt_row, void* c, void* kr, int L, int rank, int dr,
+                              int page_size, int num_pages, int* status, cudaStream_t stream) {
+  JLX_REQUIRE(L >= 0 && rank > 0 && dr >= 0 && page_size > 0, "latent_gather: bad sizes");
+  if (L == 0) return 0;
+  JLX_DISPATCH_DTYPE(dtype, T, {
+    latent_gather_kernel<T><<<L, 128, 0, stream>>>((const T*)pages, bt_row, (T*)c, (T*)kr, rank, dr, page_size, num_pages, status);
+  });
+  JLX_LAUNCH_CHECK("latent_gather");
+  return 0;
+}
+
+// k[h, t, :] = [kv_up[t, h * dn .. (h + 1) * dn) | kr[t, :]]: every head's key with the shared rotated part appended.
+template <typename T>
+__global__ void latent_key_assemble_kernel(const T* __restrict__ kv_up, long long ld_up, const T* __restrict__ kr,
+                                           T* __restrict__ k, int L, int H, int dn, int dr) {
+  JLX_TL(TL_OTHER);
+  const int t = blockIdx.x, d = dn + dr;
+  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+    const int h = i / d, e = i - h * d;
+    k[((size_t)h * L + t) * d + e] = e < dn ? kv_up[(size_t)t * ld_up + h * dn + e] : kr[(size_t)t * dr + (e - dn)];
+  }
+}
+
+JLX_API int jlx_latent_key_assemble(const void* kv_up, long long ld_up, const void* kr, void* k, int dtype, int L, int H,
+                                    int dn, int dr, cudaStream_t stream) {
+  JLX_REQUIRE(L >= 0 && H > 0 && dn > 0 && dr >= 0 && ld_up >= (long long)H * dn, "latent_key_assemble: bad sizes");
+  if (L == 0) return 0;
+  JLX_DISPATCH_DTYPE(dtype, T, {
+    latent_key_assemble_kernel<T><<<L, 256, 0, stream>>>((const T*)kv_up, ld_up, (const T*)kr, (T*)k, L, H, dn, dr);
+  });
+  JLX_LAUNCH_CHECK("latent_key_assemble");
+  return 0;
+}
+
+// p[h, i, j] = exp(scale * s[h, i, j] - m) / (sum over visible j + exp(sink_h - m)) for j <= q_start + i, else 0.
+// s: float32 [H, T, L]; p: [H, T, L] in the activations' type.  One block per (query row, head); 32-bit throughout.
+template <typename TO>
+__global__ void causal_sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, float scale,
+                                           int q_start, TO* __restrict__ p, int T, int L) {
+  JLX_TL(TL_OTHER);
+  __shared__ float scratch[33];
+  const int i = blockIdx.x, h = blockIdx.y;
+  const float* row = s + ((size_t)h * T + i) * L;
+  TO* out = p + ((size_t)h * T + i) * L;
+  const int visible = min(L, q_start + i + 1);
+  float m = sink ? sink[h] : -INFINITY;
+  for (int j = threadIdx.x; j < visible; j += blockDim.x) m = fmaxf(m, row[j] * scale);
+  // block maximum through the block sum's scratch: warp maxima, then the first warp
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = scratch[0];
+  for (int w = 1; w < (blockDim.x >> 5); ++w) m = fmaxf(m, scratch[w]);
+  float l = 0.f;
+  for (int j = threadIdx.x; j < visible; j += blockDim.x) l += expf(row[j] * scale - m);
+  l = block_sum(l, scratch) + (sink ? expf(sink[h] - m) : 0.f);
+  for (int j = threadIdx.x; j < L; j += blockDim.x) out[j] = from_f32<TO>(j < visible ? expf(row[j] * scale - m) / l : 0.f);
+}
+
+JLX_API int jlx_causal_sink_softmax(const float* s, const float* sink, float scale, int q_start, void* p, int dtype, int H,
+                                    int T, int L, cudaStream_t stream) {
+  JLX_REQUIRE(H > 0 && T >= 0 && L > 0 && q_start >= 0 && H <= 65535, "causal_sink_softmax: bad sizes");
+  if (T == 0) return 0;
+  JLX_DISPATCH_DTYPE(dtype, TO, { causal_sink_softmax_kernel<TO><<<dim3(T, H), 256, 0, stream>>>(s, sink, scale, q_start, (TO*)p, T, L); });
+  JLX_LAUNCH_CHECK("causal_sink_softmax");
   return 0;
 }
 

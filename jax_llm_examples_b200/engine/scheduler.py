@@ -113,7 +113,8 @@ class Scheduler:
 
     def _fits_empty_pool(self, n_tokens: int) -> bool:
         pages = -(-n_tokens // self.manager.page_size)
-        return (pages <= min(self.manager.num_pages(g) for g in range(len(self.manager.groups)))
+        # a model that keeps no keys and values has no page group: only the block table's width bounds a request
+        return (all(pages <= self.manager.num_pages(g) for g in range(len(self.manager.groups)))
                 and pages <= self.manager.max_pages_per_request)
 
     def plan(self) -> tuple[list[PlannedEntry], list[Request]]:

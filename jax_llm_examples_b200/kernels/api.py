@@ -266,19 +266,27 @@ def short_conv(h32: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | No
 # ------------------------------------------------------------------------------- recurrences
 def hgrn2_scan(qfv: torch.Tensor, splits: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                cu_q: torch.Tensor, slot_ids: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, out: torch.Tensor,
-               heads: int, dk: int, dv: int) -> None:
-    """The gated recurrence S = diag(f) S + (1 - f) v^T, o = S^T silu(q) over each request's tokens, with the per-head
-    RMS norm of o.  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their activations (or ``splits`` partials);
-    state: float32 [slots, H, dk, dv]; out: [N, H dv]."""
-    _contig(qfv, f_bias, lower, state, norm_weight, out)
+               heads: int, dk: int, dv: int, scratch: torch.Tensor | None = None) -> None:
+    """The gated recurrence S = diag(f) S + (1 - f) v^T, o = S^T silu(q) over each request's tokens, then the per-head
+    RMS norm of o (two launches).  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their activations (or
+    ``splits`` partials); state: float32 [slots, H, dk, dv]; out: [N, H dv]; scratch: float32 [N * H * dv] for the
+    un-normed o (made here if not given)."""
+    _contig(qfv, f_bias, lower, state, norm_weight, out, scratch)
     if any(t.dtype != torch.float32 for t in (qfv, f_bias, lower, state)) or (norm_weight is not None and norm_weight.dtype != torch.float32):
         raise KernelError("hgrn2_scan: projections, gate constants, state and norm weight must be float32")
     if tuple(state.shape[1:]) != (heads, dk, dv) or out.shape[1] != heads * dv:
         raise KernelError(f"hgrn2_scan: shapes do not fit: state {tuple(state.shape)}, out {tuple(out.shape)}")
+    N = out.shape[0]
+    if scratch is None:
+        scratch = torch.empty(N * heads * dv, dtype=torch.float32, device=out.device)
+    if scratch.dtype != torch.float32 or scratch.numel() < N * heads * dv:
+        raise KernelError("hgrn2_scan: scratch must be float32 with N * H * dv elements")
     sp, stride = _splits(qfv, splits)
+    global _launches
     _run("recurrent", "jlx_hgrn2_scan", _ptr(qfv), c_int(sp), c_longlong(stride), _ptr(f_bias), _ptr(lower), _ptr(state),
-         _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(out), c_int(code(out.dtype)),
-         c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), _stream())
+         _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(scratch), _ptr(out), c_int(code(out.dtype)),
+         c_int(N), c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), c_int(sm_count()), _stream())
+    _launches += 1  # the scan and the norm
 
 
 # -------------------------------------------------------------------------- latent attention
@@ -303,32 +311,79 @@ def latent_kv_prep(proj: torch.Tensor, splits: int, q_norm_weight: torch.Tensor,
 
 
 def latent_q_prep(q: torch.Tensor, splits: int, inv_freq: torch.Tensor, rot_dims: int, positions: torch.Tensor,
-                  q_nope: torch.Tensor, q_rot: torch.Tensor, heads: int, dn: int, dr: int) -> None:
-    """q: float32 [N, H (dn + dr)] (or partials) -> q_nope [H, N, dn] (head-major) and q_rot float32 [N, H, dr], rotated."""
-    _contig(q, inv_freq, q_nope, q_rot)
+                  q_nope: torch.Tensor, q_rot: torch.Tensor, heads: int, dn: int, dr: int, q_full: torch.Tensor | None = None) -> None:
+    """q: float32 [N, H (dn + dr)] (or partials) -> q_nope [H, N, dn] (head-major), q_rot float32 [N, H, dr], rotated,
+    and optionally q_full [H, N, dn + dr] (both parts, in q_nope's type)."""
+    _contig(q, inv_freq, q_nope, q_rot, q_full)
     N = q_rot.shape[0]
     sp, stride = _splits(q, splits)
     _run("attention_latent", "jlx_latent_q_prep", _ptr(q), c_int(sp), c_longlong(stride), _ptr(inv_freq), c_int(rot_dims),
-         _ptr(positions), _ptr(q_nope), c_int(code(q_nope.dtype)), _ptr(q_rot), c_int(N), c_int(heads), c_int(dn), c_int(dr),
-         _stream())
+         _ptr(positions), _ptr(q_nope), c_int(code(q_nope.dtype)), _ptr(q_rot), _ptr(q_full), c_int(N), c_int(heads), c_int(dn),
+         c_int(dr), _stream())
+
+
+LATENT_KEY_TILE = 32  # keys per tile of the latent attention kernel: split sizes are multiples of it
 
 
 def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                      req_of_token: torch.Tensor, positions: torch.Tensor, sink: torch.Tensor | None, out_lat: torch.Tensor,
-                     scale: float, status: torch.Tensor) -> None:
+                     scale: float, status: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int = 0, splits: int = 1,
+                     split_keys: int = 0, part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> None:
     """Causal attention in the latent space with an optional per-head sink.  q_lat: float32 [H, N, rank]; q_rot:
-    float32 [N, H, dr]; pages: [P, 1, 1, page_size, rank + dr]; out_lat: [H, N, rank]."""
-    _contig(q_lat, q_rot, pages, block_table, sink, out_lat)
+    float32 [N, H, dr]; pages: [P, 1, 1, page_size, rank + dr]; out_lat: [H, N, rank].
+    rows / n_rows: serve these token rows only (int32).  splits > 1: the keys are cut into ranges of ``split_keys``
+    (a multiple of LATENT_KEY_TILE), a block each, and a second kernel adds the ranges' results; part_acc: float32
+    [served * H * splits * rank], part_ml: float32 [served * H * splits * 2]."""
+    _contig(q_lat, q_rot, pages, block_table, sink, out_lat, rows, part_acc, part_ml)
     H, N, rank = q_lat.shape
     dr = q_rot.shape[2]
     if q_lat.dtype != torch.float32 or q_rot.dtype != torch.float32 or (sink is not None and sink.dtype != torch.float32):
         raise KernelError("attention_latent: queries and sinks must be float32")
     if pages.shape[4] != rank + dr:
         raise KernelError("attention_latent: cache rows and queries disagree in size")
+    served = n_rows if rows is not None else N
+    if splits > 1 and (part_acc is None or part_ml is None or part_acc.numel() < served * H * splits * rank
+                       or part_ml.numel() < served * H * splits * 2):
+        raise KernelError("attention_latent: scratch for the partial results is missing or too small")
+    global _launches
     _run("attention_latent", "jlx_attention_latent", _ptr(q_lat), _ptr(q_rot), _ptr(pages), c_int(code(pages.dtype)),
          _ptr(block_table), c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), _ptr(sink), _ptr(out_lat),
          c_int(code(out_lat.dtype)), c_int(N), c_int(H), c_int(rank), c_int(dr), c_int(pages.shape[3]), c_int(pages.shape[0]),
-         c_float(scale), _ptr(status), _stream())
+         c_float(scale), _ptr(rows), c_int(n_rows), c_int(splits), c_int(split_keys), _ptr(part_acc), _ptr(part_ml),
+         _ptr(status), _stream())
+    _launches += int(splits > 1)  # the combine kernel
+
+
+def latent_gather(pages: torch.Tensor, block_table_row: torch.Tensor, c: torch.Tensor, kr: torch.Tensor, status: torch.Tensor) -> None:
+    """The first L cached rows of one request (its block-table row) as two dense matrices: c [L, rank], kr [L, dr]."""
+    _contig(pages, block_table_row, c, kr)
+    L, rank = c.shape
+    dr = kr.shape[1]
+    if pages.shape[4] != rank + dr or c.dtype != pages.dtype or kr.dtype != pages.dtype:
+        raise KernelError("latent_gather: cache rows and outputs disagree")
+    _run("attention_latent", "jlx_latent_gather", _ptr(pages), c_int(code(pages.dtype)), _ptr(block_table_row), _ptr(c), _ptr(kr),
+         c_int(L), c_int(rank), c_int(dr), c_int(pages.shape[3]), c_int(pages.shape[0]), _ptr(status), _stream())
+
+
+def latent_key_assemble(kv_up: torch.Tensor, kr: torch.Tensor, k: torch.Tensor, heads: int, dn: int) -> None:
+    """k[h, t] = [kv_up[t, h dn : (h + 1) dn] | kr[t]].  kv_up: [L, >= H dn] with contiguous rows; kr: [L, dr]; k: [H, L, dn + dr]."""
+    _contig(kr, k)
+    L, dr = kr.shape
+    if kv_up.stride(1) != 1 or tuple(k.shape) != (heads, L, dn + dr) or kv_up.dtype != k.dtype:
+        raise KernelError("latent_key_assemble: shapes or types do not fit")
+    _run("attention_latent", "jlx_latent_key_assemble", _ptr(kv_up), c_longlong(kv_up.stride(0)), _ptr(kr), _ptr(k),
+         c_int(code(k.dtype)), c_int(L), c_int(heads), c_int(dn), c_int(dr), _stream())
+
+
+def causal_sink_softmax(scores: torch.Tensor, sink: torch.Tensor | None, scale: float, q_start: int, probs: torch.Tensor) -> None:
+    """probs[h, i, j] = softmax over j <= q_start + i of scale * scores[h, i, j], the denominator also holding
+    exp(sink[h]); 0 beyond the causal edge.  scores: float32 [H, T, L]; probs: [H, T, L]."""
+    _contig(scores, sink, probs)
+    H, T, L = scores.shape
+    if scores.dtype != torch.float32 or probs.shape != scores.shape:
+        raise KernelError("causal_sink_softmax: float32 scores and probabilities of the same shape are needed")
+    _run("attention_latent", "jlx_causal_sink_softmax", _ptr(scores), _ptr(sink), c_float(scale), c_int(q_start), _ptr(probs),
+         c_int(code(probs.dtype)), c_int(H), c_int(T), c_int(L), _stream())
 
 
 def heads_to_rows(x: torch.Tensor, out: torch.Tensor) -> None:

@@ -10,6 +10,7 @@ import torch
 from ..cache.manager import Retention
 from ..kernels import api as K
 from ..tracing import scope
+from .attention import plan_attention_tiles
 from .base import KVNeed, LayerCache, StepContext, StepShape, as_rows, register_part
 from .conv import ResidualShortConv
 from .linear import grouped_linear, linear
@@ -73,6 +74,8 @@ class LatentAttention(InputConvMixer):
         # per head: q_lat = W_uk[h]^T q_nope needs [rank, dn] as the product's [out, in]; v = W_uv[h] out_lat has it already
         self.w_uk_t = w_uk.reshape(H, dn, kv_rank).transpose(1, 2).contiguous()
         self.w_uv = w_uv.reshape(H, dv, kv_rank).contiguous()
+        # prompt portions (bfloat16) up-project keys and values of all heads in one product
+        self.w_ukv = torch.cat([w_uk, w_uv], dim=0).contiguous() if w_uk.dtype == torch.bfloat16 else None
         self.sink = None if sink is None else sink.to(torch.float32).contiguous()
         self.heads, self.dim, self.rot_dim, self.vdim = H, dn, dr, dv
         self.q_rank, self.kv_rank, self.scale, self.eps = q_rank, kv_rank, float(scale), float(eps)
@@ -86,13 +89,66 @@ class LatentAttention(InputConvMixer):
         return KVNeed(1, self.kv_rank + self.rot_dim, Retention.all(), planes=1)
 
     def step_planners(self):
-        return (self._planner,)
+        # the attention part's planner gives the rows of the single decoded tokens of a mixed step
+        return (self._planner, plan_attention_tiles)
+
+    # Scores of a prompt portion are made as one [H, T, L] float32 tensor per query tile; this bounds its size.
+    SCORE_TILE_BYTES = 1 << 30
+    MIN_SPLIT_KEYS = 64
+
+    def _latent_space(self, ctx: StepContext, q_lat, q_rot, cache: LayerCache, out_lat, rows=None, n_rows: int = 0) -> None:
+        """The latent-space kernel for all token rows, or the listed ones.  Few rows (decoding): the keys are cut into
+        ranges so that about two rounds of blocks fill the GPU; a second kernel adds the ranges."""
+        H = self.heads
+        served = n_rows if rows is not None else q_rot.shape[0]
+        blocks = served * -(-H // 8)
+        want = max(1, (2 * K.sm_count()) // max(blocks, 1))
+        tile = K.LATENT_KEY_TILE
+        per_split = -(-ctx.max_kv_len // want)  # keys each range would hold, rounded up to whole tiles below
+        split_keys = max(self.MIN_SPLIT_KEYS, -(-per_split // tile) * tile)
+        splits = -(-ctx.max_kv_len // split_keys)
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = ctx.workspace.get("latent_part_acc", served * H * splits * self.kv_rank, torch.float32)
+            part_ml = ctx.workspace.get("latent_part_ml", served * H * splits * 2, torch.float32)
+        K.attention_latent(q_lat, q_rot, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, self.sink, out_lat,
+                           self.scale, ctx.status, rows, n_rows, splits, split_keys, part_acc, part_ml)
+
+    def _portion(self, ctx: StepContext, cache: LayerCache, r: int, n0: int, T: int, start: int, q_full, rows_out) -> None:
+        """One request's prompt portion (rows n0 .. n0 + T, positions start ..) on the tensor cores: the request's cached
+        rows gathered, every head's keys and values up-projected from them (the library's product), scores and weighted
+        sums as per-head products (the library's, bfloat16 in, 32-bit sums), and between them this package's softmax
+        with the causal edge and the sink, in 32-bit."""
+        dt, dev = q_full.dtype, q_full.device
+        H, dn, dr, dv = self.heads, self.dim, self.rot_dim, self.vdim
+        keys = start + T
+        L = -(-keys // 8) * 8  # rows in multiples of 8 for the products; the padding is zero and no query sees it
+        c = torch.empty((L, self.kv_rank), dtype=dt, device=dev)
+        kr = torch.empty((L, dr), dtype=dt, device=dev)
+        c[keys:].zero_()
+        kr[keys:].zero_()
+        K.latent_gather(cache.pages, cache.block_table[r], c[:keys], kr[:keys], ctx.status)
+        kv_up = linear(ctx, c, self.w_ukv, dt)  # [L, H dn + H dv]
+        k = torch.empty((H, L, dn + dr), dtype=dt, device=dev)
+        K.latent_key_assemble(kv_up, kr, k, H, dn)
+        v = kv_up[:, H * dn:].unflatten(1, (H, dv)).permute(1, 0, 2)  # [H, L, dv], a view
+        tile = max(16, min(T, self.SCORE_TILE_BYTES // (4 * H * L)))
+        for t0 in range(0, T, tile):
+            t1 = min(T, t0 + tile)
+            scores = torch.bmm(q_full[:, n0 + t0:n0 + t1], k.transpose(1, 2), out_dtype=torch.float32)  # [H, t, L]
+            probs = torch.empty(scores.shape, dtype=dt, device=dev)
+            K.causal_sink_softmax(scores, self.sink, self.scale, start + t0, probs)
+            o = torch.bmm(probs, v)  # [H, t, dv]
+            K.heads_to_rows(o, rows_out[n0 + t0:n0 + t1])
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, h32: torch.Tensor | None = None):
         dt, dev = ctx.runtime.dtype, h32.device
         a, _ = self.read_input(ctx, h32, cache)
         n, H = a.shape[0], self.heads
         offsets = ctx.arrays[self._planner.array_name]
+        # prompt portions in bfloat16 go to the tensor cores, request by request (their sizes are read on the host: such
+        # a step is never captured in a graph, only steps of single tokens are)
+        portions = dt == torch.bfloat16 and ctx.max_q_len > 1 and self.w_ukv is not None
         with scope("qkv_matmul"):
             down = as_rows(linear(ctx, a, self.w_down, torch.float32, partials=True))
         cq = torch.empty((n, self.q_rank), dtype=dt, device=dev)
@@ -104,16 +160,29 @@ class LatentAttention(InputConvMixer):
             q = as_rows(linear(ctx, cq, self.w_uq, torch.float32, partials=True))
         q_nope = torch.empty((H, n, self.dim), dtype=dt, device=dev)
         q_rot = torch.empty((n, H, self.rot_dim), dtype=torch.float32, device=dev)
+        q_full = torch.empty((H, n, self.dim + self.rot_dim), dtype=dt, device=dev) if portions else None
         with scope("rope"):
-            K.latent_q_prep(q.data, q.splits, self.inv_freq, self.rot_dims, ctx.positions, q_nope, q_rot, H, self.dim, self.rot_dim)
+            K.latent_q_prep(q.data, q.splits, self.inv_freq, self.rot_dims, ctx.positions, q_nope, q_rot, H, self.dim,
+                            self.rot_dim, q_full)
+        rows = torch.empty((n, H * self.vdim), dtype=dt, device=dev)
         with scope("attention"):
-            q_lat = grouped_linear(ctx, q_nope.view(H * n, self.dim), self.w_uk_t, offsets, torch.float32, largest_group=n)
-            out_lat = torch.empty((H, n, self.kv_rank), dtype=dt, device=dev)
-            K.attention_latent(q_lat.view(H, n, self.kv_rank), q_rot, cache.pages, cache.block_table, ctx.req_of_token,
-                               ctx.positions, self.sink, out_lat, self.scale, ctx.status)
-            v = grouped_linear(ctx, out_lat.view(H * n, self.kv_rank), self.w_uv, offsets, dt, largest_group=n)
-            rows = torch.empty((n, H * self.vdim), dtype=dt, device=dev)
-            K.heads_to_rows(v.view(H, n, self.vdim), rows)
+            singles = len(ctx.host_arrays["attn_single_rows"]) if portions else n
+            if singles:
+                q_lat = grouped_linear(ctx, q_nope.view(H * n, self.dim), self.w_uk_t, offsets, torch.float32, largest_group=n)
+                out_lat = torch.empty((H, n, self.kv_rank), dtype=dt, device=dev)
+                if portions:  # only the single tokens' rows mean anything; the portions' rows are overwritten below
+                    out_lat.zero_()
+                    self._latent_space(ctx, q_lat.view(H, n, self.kv_rank), q_rot, cache, out_lat, ctx.arrays["attn_single_rows"], singles)
+                else:
+                    self._latent_space(ctx, q_lat.view(H, n, self.kv_rank), q_rot, cache, out_lat)
+                v = grouped_linear(ctx, out_lat.view(H * n, self.kv_rank), self.w_uv, offsets, dt, largest_group=n)
+                K.heads_to_rows(v.view(H, n, self.vdim), rows)
+            if portions:
+                n0 = 0
+                for r, (T, start) in enumerate(zip(ctx.host_q_lens, ctx.host_q_start)):
+                    if T > 1:
+                        self._portion(ctx, cache, r, n0, T, start, q_full, rows)
+                    n0 += T
         with scope("projection"):
             return linear(ctx, rows, self.w_o, torch.float32, partials=True)
 

@@ -78,7 +78,11 @@ def plain_logits(folder, tokens) -> np.ndarray:
     return _plain_logits(str(folder), tuple(tokens))
 
 
-TOL = {"float32": 3e-5, "bfloat16": 5e-2}
+# float32: a few thousand roundings of 6e-8 per logit.  bfloat16: activations are rounded (4e-3) several times per layer
+# run, and a tiny model's logits are sums of few terms, so single rows scatter: the mean over all rows is held tight and a
+# single row is capped where a fault (a lost state, a key off by one) would still stand out by a factor of ten.
+TOL = {"float32": 3e-5, "bfloat16": 1.2e-1}
+TOL_MEAN = {"float32": 1e-5, "bfloat16": 3e-2}
 
 
 def row_err(got: np.ndarray, ref: np.ndarray) -> float:
@@ -87,17 +91,19 @@ def row_err(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.sqrt((d ** 2).mean()) / max(np.sqrt(((ref - ref.mean()) ** 2).mean()), 1e-9))
 
 
-def compare(folder, requests: dict, got: dict, dtype: str, tol: float | None = None) -> float:
+def compare(folder, requests: dict, got: dict, dtype: str) -> float:
     """Every logit row a trace produced against the plain implementation's row at that place."""
-    worst = 0.0
+    errs = []
     for rid, toks in requests.items():
         ref = plain_logits(folder, toks)
         for pos in range(len(toks)):
             if (rid, pos) in got:
                 err = row_err(got[(rid, pos)], ref[pos])
-                assert err < (tol or TOL[dtype]), f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
-                worst = max(worst, err)
-    return worst
+                assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
+                errs.append(err)
+    mean = float(np.mean(errs))
+    assert mean < TOL_MEAN[dtype], f"{dtype}: mean relative error {mean:.3e} over {len(errs)} rows"
+    return max(errs)
 
 
 def greedy_checked(folder, prompt, got, dtype: str) -> None:
