@@ -30,6 +30,8 @@ __global__ void latent_kv_prep_kernel(const float* __restrict__ proj, int splits
                                       const int* __restrict__ positions, int q_rank, int rank, int dr, int page_size,
                                       int num_pages, int* status) {
   JLX_TL(TL_ROPE);
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int n = blockIdx.x;
   const int C = q_rank + rank + dr;
@@ -82,9 +84,9 @@ JLX_API int jlx_latent_kv_prep(const float* proj, int splits, long long split_st
   JLX_REQUIRE(eps > 0.f, "latent_kv_prep: eps must be positive");
   if (N == 0) return 0;
   JLX_DISPATCH_DTYPE(dtype, TO, {
-    latent_kv_prep_kernel<TO><<<N, 128, 0, stream>>>(proj, splits, split_stride, q_norm_w, kv_norm_w, eps, inv_freq, rot_dims,
-                                                      (TO*)cq, (TO*)pages, block_table, bt_stride, req_of_token, positions,
-                                                      q_rank, rank, dr, page_size, num_pages, status);
+    JLX_CUDA(jlx_launch_pdl(latent_kv_prep_kernel<TO>, dim3(N), dim3(128), 0, stream, proj, splits, split_stride, q_norm_w, kv_norm_w,
+                            eps, inv_freq, rot_dims, (TO*)cq, (TO*)pages, block_table, bt_stride, req_of_token, positions, q_rank,
+                            rank, dr, page_size, num_pages, status));
   });
   JLX_LAUNCH_CHECK("latent_kv_prep");
   return 0;
@@ -98,6 +100,8 @@ __global__ void latent_q_prep_kernel(const float* __restrict__ q, int splits, lo
                                      TO* __restrict__ q_nope, float* __restrict__ q_rot, TO* __restrict__ q_full, int N, int H,
                                      int dn, int dr) {
   JLX_TL(TL_ROPE);
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x, h = blockIdx.y;
   const float* row = q + ((size_t)n * H + h) * (dn + dr);
   TO* full = q_full ? q_full + ((size_t)h * N + n) * (dn + dr) : nullptr;
@@ -133,53 +137,62 @@ JLX_API int jlx_latent_q_prep(const float* q, int splits, long long split_stride
   JLX_REQUIRE(H <= 65535, "latent_q_prep: too many heads (%d)", H);
   if (N == 0) return 0;
   JLX_DISPATCH_DTYPE(dtype, TO, {
-    latent_q_prep_kernel<TO><<<dim3(N, H), 64, 0, stream>>>(q, splits, split_stride, inv_freq, rot_dims, positions, (TO*)q_nope,
-                                                            q_rot, (TO*)q_full, N, H, dn, dr);
+    JLX_CUDA(jlx_launch_pdl(latent_q_prep_kernel<TO>, dim3(N, H), dim3(64), 0, stream, q, splits, split_stride, inv_freq, rot_dims,
+                            positions, (TO*)q_nope, q_rot, (TO*)q_full, N, H, dn, dr));
   });
   JLX_LAUNCH_CHECK("latent_q_prep");
   return 0;
 }
 
 // ------------------------------------------------------------------------------------------------ attention
-// One block serves one query token and up to LAT_WARPS heads (a warp each); all of them share each tile of keys.
-// Key tiles are aligned to absolute positions (0, 32, 64, ...), so the order of a position's sums depends on the
-// position alone.  The sink opens the running maximum and denominator: m = sink, l = exp(sink - m) = 1.
+// One block serves one query token and up to LAT_WARPS * HPW heads; a warp takes HPW heads, a lane one key of the tile for
+// the scores and a slice of the latent for the weighted sums, so that every value read from shared memory serves HPW
+// products.  All heads share each tile of keys.  Key tiles are aligned to absolute positions (0, 32, 64, ...), so the
+// order of a position's sums depends on the position alone.  The sink opens the running maximum and denominator:
+// m = sink, l = exp(sink - m) = 1.
+// With `rows` the block serves token rows[blockIdx.x] (the single decoded tokens of a step that also holds prompt
+// portions).  With splits > 1 block z takes the keys [z * split_keys, (z + 1) * split_keys) (a multiple of the tile, so
+// tiles stay aligned) and leaves (m, l, unnormalised sums) for the combine kernel; the sink opens split 0.
 #define LAT_TILE 32
 #define LAT_WARPS 8
 #define LAT_MAX_R32 32  // latent size up to 1024
 
-// With `rows` the block serves token rows[blockIdx.x] (the single decoded tokens of a step that also holds prompt
-// portions).  With splits > 1 block z takes the keys [z * split_keys, (z + 1) * split_keys) (a multiple of the tile, so
-// tiles stay aligned) and leaves (m, l, unnormalised sums) for the combine kernel; the sink opens split 0.
-template <typename TC, typename TO>
+template <typename TC, typename TO, int HPW, int R32>
 __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot,
                                         const TC* __restrict__ pages, const int* __restrict__ block_table, int bt_stride,
                                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                         const float* __restrict__ sink, TO* __restrict__ out_lat, int N, int H, int rank,
                                         int dr, int page_size, int num_pages, float scale, const int* __restrict__ rows,
                                         int splits, int split_keys, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                                        int* status) {
+                                        int ldk, int* status) {
   JLX_TL(TL_ATTN_GENERIC);
-  extern __shared__ float smem[];
-  const int dk = rank + dr, ldk = dk + 1;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float smem[];
   __shared__ long long row_at[LAT_TILE];  // row number of each key of the tile in the pool, -1: a bad page
-  float* qs = smem;               // [nwarp][dk]
-  float* ks = qs + nwarp * dk;    // [LAT_TILE][dk + 1]
+  const int dk = rank + dr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float* qs = smem;                     // [nwarp * HPW][dk]
+  float* ks = qs + nwarp * HPW * dk;    // [LAT_TILE][ldk]
   const int n = rows ? rows[blockIdx.x] : blockIdx.x;
-  const int h = blockIdx.y * nwarp + warp;
+  const int h0 = (blockIdx.y * nwarp + warp) * HPW;  // the warp's first head
   const int z = blockIdx.z;
-  const bool active = h < H;
   const int p = positions[n], r = req_of_token[n];
-  if (active) {
-    for (int d = lane; d < rank; d += 32) qs[warp * dk + d] = q_lat[((size_t)h * N + n) * rank + d];
-    for (int d = lane; d < dr; d += 32) qs[warp * dk + rank + d] = q_rot[((size_t)n * H + h) * dr + d];
+  for (int u = 0; u < HPW; ++u) {  // heads beyond H get a zero query: they run along and write nothing
+    const int h = h0 + u;
+    float* q = qs + (warp * HPW + u) * dk;
+    for (int d = lane; d < rank; d += 32) q[d] = h < H ? q_lat[((size_t)h * N + n) * rank + d] : 0.f;
+    for (int d = lane; d < dr; d += 32) q[rank + d] = h < H ? q_rot[((size_t)n * H + h) * dr + d] : 0.f;
   }
   const bool has_sink = sink != nullptr && z == 0;
-  float m = (active && has_sink) ? sink[h] : -INFINITY, l = has_sink ? 1.f : 0.f;
-  float acc[LAT_MAX_R32];
+  float m[HPW], l[HPW], acc[HPW][R32];
 #pragma unroll
-  for (int i = 0; i < LAT_MAX_R32; ++i) acc[i] = 0.f;
+  for (int u = 0; u < HPW; ++u) {
+    m[u] = (has_sink && h0 + u < H) ? sink[h0 + u] : -INFINITY;
+    l[u] = has_sink ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < R32; ++i) acc[u][i] = 0.f;
+  }
   const int nd = (rank + 31) >> 5;
   const int t_begin = splits > 1 ? z * split_keys : 0;
   const int t_end = splits > 1 ? min(p, (z + 1) * split_keys - 1) : p;  // last key of this block
@@ -187,6 +200,7 @@ __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const f
   // 16-byte loads of the cached rows where their size and the pool's address allow
   constexpr int VEC = 16 / (int)sizeof(TC);
   const bool wide = (dk % VEC) == 0 && ((uintptr_t)pages & 15) == 0;
+  const bool quads = (dk & 3) == 0 && (ldk & 3) == 0;  // scores with 16-byte reads of shared memory
   bool bad_page = false;
   for (int t0 = t_begin; t0 <= t_end; t0 += LAT_TILE) {
     __syncthreads();  // the previous tile is consumed; qs is visible
@@ -219,55 +233,83 @@ __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const f
       }
     }
     __syncthreads();
-    if (active) {
-      float s = -INFINITY;
-      if (lane < cnt) {
-        // four running sums (in a fixed order), so that the products do not wait for one another
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-        const float* kr = ks + lane * ldk;
-        const float* qr = qs + warp * dk;
-        int d = 0;
-        for (; d + 3 < dk; d += 4) {
-          d0 = fmaf(qr[d], kr[d], d0);
-          d1 = fmaf(qr[d + 1], kr[d + 1], d1);
-          d2 = fmaf(qr[d + 2], kr[d + 2], d2);
-          d3 = fmaf(qr[d + 3], kr[d + 3], d3);
+    float sc[HPW];
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) sc[u] = -INFINITY;
+    if (lane < cnt) {
+      float dot[HPW];
+#pragma unroll
+      for (int u = 0; u < HPW; ++u) dot[u] = 0.f;
+      const float* kr = ks + lane * ldk;
+      const float* qr = qs + warp * HPW * dk;
+      if (quads) {
+        for (int d = 0; d < dk; d += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+          for (int u = 0; u < HPW; ++u) {
+            const float4 qv = *reinterpret_cast<const float4*>(qr + u * dk + d);
+            dot[u] = fmaf(qv.x, kv.x, dot[u]);
+            dot[u] = fmaf(qv.y, kv.y, dot[u]);
+            dot[u] = fmaf(qv.z, kv.z, dot[u]);
+            dot[u] = fmaf(qv.w, kv.w, dot[u]);
+          }
         }
-        for (; d < dk; ++d) d0 = fmaf(qr[d], kr[d], d0);
-        s = ((d0 + d1) + (d2 + d3)) * scale;
+      } else {
+        for (int d = 0; d < dk; ++d) {
+          const float kv = kr[d];
+#pragma unroll
+          for (int u = 0; u < HPW; ++u) dot[u] = fmaf(qr[u * dk + d], kv, dot[u]);
+        }
       }
-      const float m_new = fmaxf(m, warp_max(s));
-      const float corr = expf(m - m_new);  // without a sink m is -inf on the first tile: exp(-inf) = 0
-      const float pj = lane < cnt ? expf(s - m_new) : 0.f;
-      l = l * corr + warp_sum(pj);
-      m = m_new;
 #pragma unroll
-      for (int i = 0; i < LAT_MAX_R32; ++i) acc[i] *= corr;
-      for (int j = 0; j < cnt; ++j) {  // key by key: the lane's entries of the latent are independent sums
-        const float pv = __shfl_sync(0xffffffffu, pj, j);
-        const float* kj = ks + j * ldk + lane;
+      for (int u = 0; u < HPW; ++u) sc[u] = dot[u] * scale;
+    }
+    float pj[HPW];
 #pragma unroll
-        for (int i = 0; i < LAT_MAX_R32; ++i)
-          if (i < nd && lane + 32 * i < rank) acc[i] = fmaf(pv, kj[32 * i], acc[i]);
+    for (int u = 0; u < HPW; ++u) {
+      const float m_new = fmaxf(m[u], warp_max(sc[u]));
+      const float corr = expf(m[u] - m_new);  // without a sink m is -inf on the first tile: exp(-inf) = 0
+      pj[u] = lane < cnt ? expf(sc[u] - m_new) : 0.f;
+      l[u] = l[u] * corr + warp_sum(pj[u]);
+      m[u] = m_new;
+#pragma unroll
+      for (int i = 0; i < R32; ++i) acc[u][i] *= corr;
+    }
+    for (int j = 0; j < cnt; ++j) {  // key by key: the lane's entries of the latent are independent sums
+      float pv[HPW];
+#pragma unroll
+      for (int u = 0; u < HPW; ++u) pv[u] = __shfl_sync(0xffffffffu, pj[u], j);
+      const float* kj = ks + j * ldk + lane;
+#pragma unroll
+      for (int i = 0; i < R32; ++i) {
+        if (i < nd && lane + 32 * i < rank) {
+          const float kv = kj[32 * i];
+#pragma unroll
+          for (int u = 0; u < HPW; ++u) acc[u][i] = fmaf(pv[u], kv, acc[u][i]);
+        }
       }
     }
   }
   if (bad_page) atomicOr(status, JLX_STATUS_BAD_PAGE);
-  if (!active) return;
-  if (splits > 1) {
-    const size_t slot = ((size_t)blockIdx.x * H + h) * splits + z;
-    if (lane == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
 #pragma unroll
-    for (int i = 0; i < LAT_MAX_R32; ++i) {
-      const int d = lane + 32 * i;
-      if (i < nd && d < rank) part_acc[slot * rank + d] = acc[i];
+  for (int u = 0; u < HPW; ++u) {
+    const int h = h0 + u;
+    if (h >= H) continue;
+    if (splits > 1) {
+      const size_t slot = ((size_t)blockIdx.x * H + h) * splits + z;
+      if (lane == 0) { part_ml[2 * slot] = m[u]; part_ml[2 * slot + 1] = l[u]; }
+#pragma unroll
+      for (int i = 0; i < R32; ++i) {
+        const int d = lane + 32 * i;
+        if (i < nd && d < rank) part_acc[slot * rank + d] = acc[u][i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < R32; ++i) {
+        const int d = lane + 32 * i;
+        if (i < nd && d < rank) out_lat[((size_t)h * N + n) * rank + d] = from_f32<TO>(acc[u][i] / l[u]);
+      }
     }
-    return;
-  }
-#pragma unroll
-  for (int i = 0; i < LAT_MAX_R32; ++i) {
-    const int d = lane + 32 * i;
-    if (i < nd && d < rank) out_lat[((size_t)h * N + n) * rank + d] = from_f32<TO>(acc[i] / l);
   }
 }
 
@@ -277,6 +319,8 @@ __global__ void attention_latent_combine_kernel(const float* __restrict__ part_a
                                                 TO* __restrict__ out_lat, const int* __restrict__ rows, int N, int H, int rank,
                                                 int splits) {
   JLX_TL(TL_ATTN_COMBINE);
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const int n = rows ? rows[b] : b;
   const size_t slot0 = ((size_t)b * H + h) * splits;
@@ -311,23 +355,38 @@ JLX_API int jlx_attention_latent(const float* q_lat, const float* q_rot, const v
               "attention_latent: splits need a key count that is a multiple of %d, and scratch", LAT_TILE);
   const int served = rows ? n_rows : N;
   if (served == 0) return 0;
-  const int nwarp = H < LAT_WARPS ? H : LAT_WARPS;
   const int dk = rank + dr;
-  const size_t smem = sizeof(float) * ((size_t)nwarp * dk + (size_t)LAT_TILE * (dk + 1));
+  // a key's row in shared memory: padded so that 16-byte reads of a quarter warp's rows fall into different banks
+  // (rows a multiple of 4 floats apart with an odd count of 16-byte pieces), else by one float
+  const int ldk = (dk & 3) == 0 ? (((dk >> 2) & 1) ? dk : dk + 4) : dk + 1;
+  const bool big = rank > 512;             // latents above 512: two heads per warp, else four
+  const int hpw = big ? 2 : 4;
+  const int groups = (H + hpw - 1) / hpw;  // warps' worth of heads
+  const int nwarp = groups < LAT_WARPS ? groups : LAT_WARPS;
+  const size_t smem = sizeof(float) * ((size_t)nwarp * hpw * dk + (size_t)LAT_TILE * ldk);
   JLX_REQUIRE(smem <= 200 * 1024, "attention_latent: a key tile of %d x %d does not fit into shared memory", LAT_TILE, dk);
-  const int hb = (H + nwarp - 1) / nwarp;
+  const int hb = (groups + nwarp - 1) / nwarp;
   JLX_REQUIRE(hb <= 65535 && H <= 65535, "attention_latent: too many heads (%d)", H);
+#define LAT_GO(HPW, R32)                                                                                                   \
+  do {                                                                                                                     \
+    if (smem > 48 * 1024)                                                                                                  \
+      JLX_CUDA(cudaFuncSetAttribute(attention_latent_kernel<TC, TO, HPW, R32>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                    (int)smem));                                                                           \
+    JLX_CUDA(jlx_launch_pdl(attention_latent_kernel<TC, TO, HPW, R32>, dim3(served, hb, splits), dim3(nwarp * 32), smem, stream, \
+                            q_lat, q_rot, (const TC*)pages, block_table, bt_stride, req_of_token, positions, sink, (TO*)out_lat, \
+                            N, H, rank, dr, page_size, num_pages, scale, rows, splits, split_keys, part_acc, part_ml, ldk,  \
+                            status));                                                                                      \
+  } while (0)
   JLX_DISPATCH_DTYPE(cache_dtype, TC, JLX_DISPATCH_DTYPE(out_dtype, TO, {
-    if (smem > 48 * 1024)
-      JLX_CUDA(cudaFuncSetAttribute(attention_latent_kernel<TC, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attention_latent_kernel<TC, TO><<<dim3(served, hb, splits), nwarp * 32, smem, stream>>>(
-        q_lat, q_rot, (const TC*)pages, block_table, bt_stride, req_of_token, positions, sink, (TO*)out_lat, N, H, rank, dr,
-        page_size, num_pages, scale, rows, splits, split_keys, part_acc, part_ml, status);
+    if (big) LAT_GO(2, 32);
+    else LAT_GO(4, 16);
   }));
+#undef LAT_GO
   JLX_LAUNCH_CHECK("attention_latent");
   if (splits > 1) {
     JLX_DISPATCH_DTYPE(out_dtype, TO, {
-      attention_latent_combine_kernel<TO><<<dim3(served, H), 128, 0, stream>>>(part_acc, part_ml, (TO*)out_lat, rows, N, H, rank, splits);
+      JLX_CUDA(jlx_launch_pdl(attention_latent_combine_kernel<TO>, dim3(served, H), dim3(128), 0, stream, (const float*)part_acc,
+                              (const float*)part_ml, (TO*)out_lat, rows, N, H, rank, splits));
     });
     JLX_LAUNCH_CHECK("attention_latent_combine");
   }
@@ -391,18 +450,38 @@ JLX_API int jlx_latent_key_assemble(const void* kv_up, long long ld_up, const vo
 
 // p[h, i, j] = exp(scale * s[h, i, j] - m) / (sum over visible j + exp(sink_h - m)) for j <= q_start + i, else 0.
 // s: float32 [H, T, L]; p: [H, T, L] in the activations' type.  One block per (query row, head); 32-bit throughout.
+// With `staged` the visible part of the row is read once into shared memory (L floats) and the three passes run there.
 template <typename TO>
 __global__ void causal_sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, float scale,
-                                           int q_start, TO* __restrict__ p, int T, int L) {
+                                           int q_start, TO* __restrict__ p, int T, int L, int staged) {
   JLX_TL(TL_OTHER);
+  extern __shared__ __align__(16) float stage[];
   __shared__ float scratch[33];
   const int i = blockIdx.x, h = blockIdx.y;
   const float* row = s + ((size_t)h * T + i) * L;
   TO* out = p + ((size_t)h * T + i) * L;
   const int visible = min(L, q_start + i + 1);
   float m = sink ? sink[h] : -INFINITY;
-  for (int j = threadIdx.x; j < visible; j += blockDim.x) m = fmaxf(m, row[j] * scale);
-  // block maximum through the block sum's scratch: warp maxima, then the first warp
+  if (staged) {
+    if ((L & 3) == 0) {  // rows start on 16-byte boundaries
+      for (int j = threadIdx.x * 4; j < visible; j += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(row + j);
+        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+        *reinterpret_cast<float4*>(stage + j) = v;
+        m = fmaxf(m, v.x);
+        if (j + 1 < visible) m = fmaxf(m, v.y);
+        if (j + 2 < visible) m = fmaxf(m, v.z);
+        if (j + 3 < visible) m = fmaxf(m, v.w);
+      }
+    } else {
+      for (int j = threadIdx.x; j < visible; j += blockDim.x) { stage[j] = row[j] * scale; m = fmaxf(m, stage[j]); }
+    }
+    row = stage;
+    scale = 1.f;
+  } else {
+    for (int j = threadIdx.x; j < visible; j += blockDim.x) m = fmaxf(m, row[j] * scale);
+  }
+  // the block's maximum: warp maxima, then every thread takes the largest
   m = warp_max(m);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
@@ -419,7 +498,13 @@ JLX_API int jlx_causal_sink_softmax(const float* s, const float* sink, float sca
                                     int T, int L, cudaStream_t stream) {
   JLX_REQUIRE(H > 0 && T >= 0 && L > 0 && q_start >= 0 && H <= 65535, "causal_sink_softmax: bad sizes");
   if (T == 0) return 0;
-  JLX_DISPATCH_DTYPE(dtype, TO, { causal_sink_softmax_kernel<TO><<<dim3(T, H), 256, 0, stream>>>(s, sink, scale, q_start, (TO*)p, T, L); });
+  const int staged = (size_t)L * 4 <= 160 * 1024;
+  const size_t smem = staged ? (size_t)(L + 4) * 4 : 0;
+  JLX_DISPATCH_DTYPE(dtype, TO, {
+    if (smem > 48 * 1024)
+      JLX_CUDA(cudaFuncSetAttribute(causal_sink_softmax_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    causal_sink_softmax_kernel<TO><<<dim3(T, H), 256, smem, stream>>>(s, sink, scale, q_start, (TO*)p, T, L, staged);
+  });
   JLX_LAUNCH_CHECK("causal_sink_softmax");
   return 0;
 }
@@ -428,6 +513,8 @@ JLX_API int jlx_causal_sink_softmax(const float* s, const float* sink, float sca
 template <typename T>
 __global__ void heads_to_rows_kernel(const T* __restrict__ in, T* __restrict__ out, int N, int H, int d) {
   JLX_TL(TL_OTHER);
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
     const int h = i / d, c = i - h * d;
@@ -438,7 +525,7 @@ __global__ void heads_to_rows_kernel(const T* __restrict__ in, T* __restrict__ o
 JLX_API int jlx_heads_to_rows(const void* in, void* out, int dtype, int N, int H, int d, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && H > 0 && d > 0, "heads_to_rows: bad sizes");
   if (N == 0) return 0;
-  JLX_DISPATCH_DTYPE(dtype, T, { heads_to_rows_kernel<T><<<N, 256, 0, stream>>>((const T*)in, (T*)out, N, H, d); });
+  JLX_DISPATCH_DTYPE(dtype, T, { JLX_CUDA(jlx_launch_pdl(heads_to_rows_kernel<T>, dim3(N), dim3(256), 0, stream, (const T*)in, (T*)out, N, H, d)); });
   JLX_LAUNCH_CHECK("heads_to_rows");
   return 0;
 }

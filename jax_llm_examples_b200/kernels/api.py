@@ -264,29 +264,36 @@ def short_conv(h32: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | No
 
 
 # ------------------------------------------------------------------------------- recurrences
+def hgrn2_scan_scratch(n_tokens: int, heads: int, dk: int, dv: int) -> int:
+    """float32 elements of scratch that ``hgrn2_scan`` needs: the gated rows and the un-normed outputs."""
+    return -(-n_tokens * heads * (2 * dk + dv) // 4) * 4 + n_tokens * heads * dv
+
+
 def hgrn2_scan(qfv: torch.Tensor, splits: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                cu_q: torch.Tensor, slot_ids: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, out: torch.Tensor,
                heads: int, dk: int, dv: int, scratch: torch.Tensor | None = None) -> None:
     """The gated recurrence S = diag(f) S + (1 - f) v^T, o = S^T silu(q) over each request's tokens, then the per-head
-    RMS norm of o (two launches).  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their activations (or
-    ``splits`` partials); state: float32 [slots, H, dk, dv]; out: [N, H dv]; scratch: float32 [N * H * dv] for the
-    un-normed o (made here if not given)."""
+    RMS norm of o (three launches: gates, scan, norm).  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their
+    activations (or ``splits`` partials); state: float32 [slots, H, dk, dv]; out: [N, H dv]; scratch: float32 of
+    ``hgrn2_scan_scratch`` elements (made here if not given)."""
     _contig(qfv, f_bias, lower, state, norm_weight, out, scratch)
     if any(t.dtype != torch.float32 for t in (qfv, f_bias, lower, state)) or (norm_weight is not None and norm_weight.dtype != torch.float32):
         raise KernelError("hgrn2_scan: projections, gate constants, state and norm weight must be float32")
     if tuple(state.shape[1:]) != (heads, dk, dv) or out.shape[1] != heads * dv:
         raise KernelError(f"hgrn2_scan: shapes do not fit: state {tuple(state.shape)}, out {tuple(out.shape)}")
     N = out.shape[0]
+    need = hgrn2_scan_scratch(N, heads, dk, dv)
     if scratch is None:
-        scratch = torch.empty(N * heads * dv, dtype=torch.float32, device=out.device)
-    if scratch.dtype != torch.float32 or scratch.numel() < N * heads * dv:
-        raise KernelError("hgrn2_scan: scratch must be float32 with N * H * dv elements")
+        scratch = torch.empty(need, dtype=torch.float32, device=out.device)
+    if scratch.dtype != torch.float32 or scratch.numel() < need or scratch.data_ptr() % 16:
+        raise KernelError("hgrn2_scan: scratch must be float32, 16-byte aligned, with hgrn2_scan_scratch() elements")
+    gates, o32 = scratch, scratch[need - N * heads * dv:]
     sp, stride = _splits(qfv, splits)
     global _launches
     _run("recurrent", "jlx_hgrn2_scan", _ptr(qfv), c_int(sp), c_longlong(stride), _ptr(f_bias), _ptr(lower), _ptr(state),
-         _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(scratch), _ptr(out), c_int(code(out.dtype)),
+         _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(gates), _ptr(o32), _ptr(out), c_int(code(out.dtype)),
          c_int(N), c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), c_int(sm_count()), _stream())
-    _launches += 1  # the scan and the norm
+    _launches += 2  # the gates, the scan and the norm
 
 
 # -------------------------------------------------------------------------- latent attention

@@ -94,6 +94,7 @@ class LatentAttention(InputConvMixer):
 
     # Scores of a prompt portion are made as one [H, T, L] float32 tensor per query tile; this bounds its size.
     SCORE_TILE_BYTES = 1 << 30
+    QUERY_TILE = 512  # query rows of a portion per score product
     MIN_SPLIT_KEYS = 64
 
     def _latent_space(self, ctx: StepContext, q_lat, q_rot, cache: LayerCache, out_lat, rows=None, n_rows: int = 0) -> None:
@@ -101,7 +102,8 @@ class LatentAttention(InputConvMixer):
         ranges so that about two rounds of blocks fill the GPU; a second kernel adds the ranges."""
         H = self.heads
         served = n_rows if rows is not None else q_rot.shape[0]
-        blocks = served * -(-H // 8)
+        per_block = 8 * (2 if self.kv_rank > 512 else 4)  # heads a block of the kernel serves (csrc/attention_latent.cu)
+        blocks = served * -(-H // per_block)
         want = max(1, (2 * K.sm_count()) // max(blocks, 1))
         tile = K.LATENT_KEY_TILE
         per_split = -(-ctx.max_kv_len // want)  # keys each range would hold, rounded up to whole tiles below
@@ -132,13 +134,15 @@ class LatentAttention(InputConvMixer):
         k = torch.empty((H, L, dn + dr), dtype=dt, device=dev)
         K.latent_key_assemble(kv_up, kr, k, H, dn)
         v = kv_up[:, H * dn:].unflatten(1, (H, dv)).permute(1, 0, 2)  # [H, L, dv], a view
-        tile = max(16, min(T, self.SCORE_TILE_BYTES // (4 * H * L)))
+        # query tiles: each sees the keys up to its own last row only (the rest of the causal triangle is not computed)
+        tile = max(16, min(self.QUERY_TILE, self.SCORE_TILE_BYTES // (4 * H * L)))
         for t0 in range(0, T, tile):
             t1 = min(T, t0 + tile)
-            scores = torch.bmm(q_full[:, n0 + t0:n0 + t1], k.transpose(1, 2), out_dtype=torch.float32)  # [H, t, L]
+            Lt = min(L, -(-(start + t1) // 8) * 8)
+            scores = torch.bmm(q_full[:, n0 + t0:n0 + t1], k[:, :Lt].transpose(1, 2), out_dtype=torch.float32)  # [H, t, Lt]
             probs = torch.empty(scores.shape, dtype=dt, device=dev)
             K.causal_sink_softmax(scores, self.sink, self.scale, start + t0, probs)
-            o = torch.bmm(probs, v)  # [H, t, dv]
+            o = torch.bmm(probs, v[:, :Lt])  # [H, t, dv]
             K.heads_to_rows(o, rows_out[n0 + t0:n0 + t1])
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, h32: torch.Tensor | None = None):

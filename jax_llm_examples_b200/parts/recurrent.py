@@ -69,7 +69,8 @@ class HGRN2(InputConvMixer):
             qfv = as_rows(linear(ctx, a, self.w_qfv, torch.float32, partials=True))
         o = torch.empty((a.shape[0], self.heads * self.vdim), dtype=ctx.runtime.dtype, device=a.device)
         with scope("attention"):
-            scratch = ctx.workspace.get("hgrn2_o", a.shape[0] * self.heads * self.vdim, torch.float32) if ctx.workspace else None
+            need = K.hgrn2_scan_scratch(a.shape[0], self.heads, self.dim, self.vdim)
+            scratch = ctx.workspace.get("hgrn2_scan", need, torch.float32) if ctx.workspace else None
             K.hgrn2_scan(qfv.data, qfv.splits, self.f_bias, self.lower, state, ctx.cu_q, ctx.slot_ids, self.norm_weight,
                          self.eps, o, self.heads, self.dim, self.vdim, scratch)
         with scope("projection"):
