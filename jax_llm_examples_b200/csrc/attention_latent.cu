@@ -30,7 +30,7 @@ __global__ void latent_kv_prep_kernel(const float* __restrict__ proj, int splits
                                       const int* __restrict__ positions, int q_rank, int rank, int dr, int page_size,
                                       int num_pages, int* status) {
   JLX_TL(TL_ROPE);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   __shared__ float scratch[33];
   const int n = blockIdx.x;
@@ -100,7 +100,7 @@ __global__ void latent_q_prep_kernel(const float* __restrict__ q, int splits, lo
                                      TO* __restrict__ q_nope, float* __restrict__ q_rot, TO* __restrict__ q_full, int N, int H,
                                      int dn, int dr) {
   JLX_TL(TL_ROPE);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int n = blockIdx.x, h = blockIdx.y;
   const float* row = q + ((size_t)n * H + h) * (dn + dr);
@@ -166,7 +166,7 @@ __global__ void attention_latent_kernel(const float* __restrict__ q_lat, const f
                                         int splits, int split_keys, float* __restrict__ part_acc, float* __restrict__ part_ml,
                                         int ldk, int* status) {
   JLX_TL(TL_ATTN_GENERIC);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
   __shared__ long long row_at[LAT_TILE];  // row number of each key of the tile in the pool, -1: a bad page
@@ -319,7 +319,7 @@ __global__ void attention_latent_combine_kernel(const float* __restrict__ part_a
                                                 TO* __restrict__ out_lat, const int* __restrict__ rows, int N, int H, int rank,
                                                 int splits) {
   JLX_TL(TL_ATTN_COMBINE);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const int n = rows ? rows[b] : b;
@@ -513,7 +513,7 @@ JLX_API int jlx_causal_sink_softmax(const float* s, const float* sink, float sca
 template <typename T>
 __global__ void heads_to_rows_kernel(const T* __restrict__ in, T* __restrict__ out, int N, int H, int d) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int n = blockIdx.x;
   for (int i = threadIdx.x; i < H * d; i += blockDim.x) {

@@ -32,7 +32,7 @@ __global__ void group_norm_kernel(float* __restrict__ x, const float* __restrict
                                   TO* __restrict__ out, long long ld_out, float* __restrict__ out32,
                                   const int* __restrict__ row_index, int D) {
   JLX_TL(TL_NORM);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   extern __shared__ float smem[];
   float* row = smem;       // [D]
@@ -105,7 +105,7 @@ __global__ void group_norm_x4_kernel(float* __restrict__ x, const float* __restr
                                      TO* __restrict__ out, long long ld_out, float* __restrict__ out32,
                                      const int* __restrict__ row_index, int D) {
   JLX_TL(TL_NORM);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
   float* row = smem;       // [D]
@@ -231,7 +231,7 @@ template <typename TI, typename TO>
 __global__ void bias_act_kernel(const TI* __restrict__ in, int splits, long long split_stride, const float* __restrict__ bias,
                                 const float* __restrict__ add, int act, TO* __restrict__ out, int F) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t i = blockIdx.x;
   for (int f = threadIdx.x; f < F; f += blockDim.x) {
@@ -248,7 +248,7 @@ template <typename TO>
 __global__ void bias_act_f32x4_kernel(const float* __restrict__ in, int splits, long long split_stride, const float* __restrict__ bias,
                                       const float* __restrict__ add, int act, TO* __restrict__ out, int F) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t i = blockIdx.x;
   for (int f = threadIdx.x * 4; f < F; f += blockDim.x * 4) {
@@ -308,7 +308,7 @@ __global__ void short_conv_kernel(const float* __restrict__ h, const float* __re
                                   const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                   TO* __restrict__ out, int N, int D, int taps) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int b = blockIdx.x;
   if (b < N) {
@@ -352,7 +352,7 @@ __global__ void short_conv_x4_kernel(const float* __restrict__ h, const float* _
                                      const int* __restrict__ req_of_token, const int* __restrict__ positions,
                                      TO* __restrict__ out, int N, int D, int taps) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int b = blockIdx.x, D4 = D >> 2;
   auto h4 = [&](int row, int d) { return reinterpret_cast<const float4*>(h + (size_t)row * D)[d]; };

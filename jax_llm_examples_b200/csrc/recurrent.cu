@@ -41,7 +41,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __global__ void hgrn2_gates_kernel(const float* __restrict__ qfv, int splits, long long split_stride, const float* __restrict__ f_bias,
                                    const float* __restrict__ lower, float* __restrict__ g, int HK, int HV) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t n = blockIdx.x;
   const int C = 2 * HK + HV;
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(512)
 hgrn2_scan_kernel(const float* __restrict__ g, float* __restrict__ state, const int* __restrict__ cu_q,
                   const int* __restrict__ slot_ids, float* __restrict__ o32, int H, int dk, int dv, int DVB) {
   JLX_TL(TL_OTHER);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
   const int dkp = NSP * REC_RT;         // dk padded to whole row slices
@@ -231,7 +231,7 @@ template <typename TO>
 __global__ void head_rms_norm_kernel(const float* __restrict__ o32, const float* __restrict__ w, float eps, TO* __restrict__ out,
                                      int rows, int dv) {
   JLX_TL(TL_NORM);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
