@@ -568,7 +568,10 @@ def run_compare(args) -> dict:
                 "llama add_rmsnorm": frac(l["decode_kernels_ms"].get("jlx_add_rmsnorm", 0), (2 * layers + 1) * B * width * 14),
             },
             "prefill": {
-                "tebivik attention_latent": frac(t["prefill_kernels_ms"].get("jlx_attention_latent", 0), 0, att_runs * heads * P * P / 2 * 2 * (2 * rank + dr)),
+                # the softmax between the two per-head products of a prompt portion: float32 scores in, bfloat16 weights out,
+                # query tiles of 512 rows against the keys up to the tile's last row
+                "tebivik causal_sink_softmax": frac(t["prefill_kernels_ms"].get("jlx_causal_sink_softmax", 0),
+                                                    att_runs * heads * sum(min(512, P - t0) * min(P, t0 + 512) for t0 in range(0, P, 512)) * 6),
                 "tebivik hgrn2_scan": frac(t["prefill_kernels_ms"].get("jlx_hgrn2_scan", 0), rec_runs * P * (2 * heads * 128 + heads * 128) * 4, 0),
                 "tebivik group_norm": frac(t["prefill_kernels_ms"].get("jlx_group_norm", 0), (2 * runs + 1) * P * width * 14),
                 "llama attention_prefill_tc": frac(l["prefill_kernels_ms"].get("jlx_attention_prefill_tc", 0), 0, layers * heads * P * P / 2 * 4 * dh),

@@ -96,6 +96,7 @@ class LatentAttention(InputConvMixer):
     SCORE_TILE_BYTES = 1 << 30
     QUERY_TILE = 512  # query rows of a portion per score product
     MIN_SPLIT_KEYS = 64
+    SPLIT_ROUNDS = 2  # blocks per multiprocessor that the key ranges of a decode step aim at
 
     def _latent_space(self, ctx: StepContext, q_lat, q_rot, cache: LayerCache, out_lat, rows=None, n_rows: int = 0) -> None:
         """The latent-space kernel for all token rows, or the listed ones.  Few rows (decoding): the keys are cut into
@@ -104,7 +105,7 @@ class LatentAttention(InputConvMixer):
         served = n_rows if rows is not None else q_rot.shape[0]
         per_block = 8 * (2 if self.kv_rank > 512 else 4)  # heads a block of the kernel serves (csrc/attention_latent.cu)
         blocks = served * -(-H // per_block)
-        want = max(1, (2 * K.sm_count()) // max(blocks, 1))
+        want = max(1, (self.SPLIT_ROUNDS * K.sm_count()) // max(blocks, 1))
         tile = K.LATENT_KEY_TILE
         per_split = -(-ctx.max_kv_len // want)  # keys each range would hold, rounded up to whole tiles below
         split_keys = max(self.MIN_SPLIT_KEYS, -(-per_split // tile) * tile)

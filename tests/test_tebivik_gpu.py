@@ -74,14 +74,15 @@ def test_group_norm_kernel_closes_one_sublayer_and_opens_the_next(D, groups, spl
     _close(o4, (x + part.sum(0)), 3e-6, "plain sum")
 
 
+@pytest.mark.parametrize("D", [40, 38])  # four channels per thread, and one
 @pytest.mark.parametrize("taps", [1, 2, 4])
-def test_short_conv_carries_its_last_inputs_across_portions_of_any_size(taps):
+def test_short_conv_carries_its_last_inputs_across_portions_of_any_size(taps, D):
     """Three requests of unequal length in portions down to one token, interleaved in one batch; state slots given
     in another order than the requests; a slot used again after it was cleared."""
     from jax_llm_examples_b200.parts import ResidualShortConv, Runtime
 
     torch.manual_seed(taps)
-    D, rt = 40, Runtime(torch.float32, torch.device(DEV))
+    rt = Runtime(torch.float32, torch.device(DEV))
     conv = ResidualShortConv(torch.randn(D, taps, device=DEV))
     need = conv.state_need()
     assert (need is None) == (taps == 1)
@@ -240,6 +241,37 @@ def test_latent_attention_kernel_sees_a_far_key_and_nothing_beyond_the_query():
             _close(out[h, 0], ref, 1e-4, f"sink of head {h} at {qpos}")
         assert float(out[1, 0].norm()) < 0.01 * float(out[0, 0].norm())  # exp(40 - 30) outweighs every key
     assert int(status) == 0
+
+
+@pytest.mark.parametrize("T, L, start", [(5, 12, 7), (16, 64, 48), (3, 37, 0), (9, 203, 150)])
+def test_prompt_softmax_stops_at_the_causal_edge_and_counts_the_sink_once(T, L, start):
+    """The softmax between the two products of a prompt portion: query row i (position start + i) weighs the keys up to
+    its own position.  The key right behind the edge gets by far the largest score; it must weigh nothing.  The sink
+    adds exp(sink) to the denominator, unscaled, once."""
+    from jax_llm_examples_b200.kernels import api as K
+
+    torch.manual_seed(L)
+    H_, scale = 3, 0.37
+    s = torch.randn(H_, T, L, device=DEV)
+    for i in range(T):
+        if start + i + 1 < L:
+            s[:, i, start + i + 1] = 80.0  # just outside
+        s[:, i, start + i] += 3.0  # just inside: the query's own position
+    sink = torch.tensor([-1.0, 0.5, 6.0], device=DEV)
+    for out_dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 5e-3)):
+        p = torch.full((H_, T, L), 7.0, device=DEV, dtype=out_dtype)
+        K.causal_sink_softmax(s, sink, scale, start, p)
+        ref = torch.zeros(H_, T, L, dtype=torch.float64)
+        for i in range(T):
+            vis = min(L, start + i + 1)
+            z = s[:, i, :vis].double().cpu() * scale
+            e = torch.exp(z - z.max(dim=-1, keepdim=True).values)
+            ref[:, i, :vis] = e / (e.sum(-1, keepdim=True) + torch.exp(sink.double().cpu()[:, None] - z.max(dim=-1, keepdim=True).values))
+        assert float((p.double().cpu() - ref).abs().max()) < tol
+        assert float(p[:, 0, min(L - 1, start + 1):].float().abs().max()) == 0.0 or start + 1 >= L
+    p0 = torch.empty(H_, T, L, device=DEV)
+    K.causal_sink_softmax(s, None, scale, start, p0)  # without a sink the visible weights sum to one
+    assert torch.allclose(p0.sum(-1), torch.ones(H_, T, device=DEV), atol=1e-5)
 
 
 @pytest.mark.parametrize("name, dtype, tol", DTYPES)
