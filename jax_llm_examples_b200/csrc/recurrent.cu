@@ -83,7 +83,7 @@ __device__ __forceinline__ float2 sub2(float2 a, float2 b) {
 template <bool SEG>
 __device__ __forceinline__ void rec_token(const float* __restrict__ row, int dkp, int i0, int jl,
                                           float2 (&S)[REC_RT / 2][REC_CT], float (&acc)[REC_CT], float2 (&cum)[REC_RT / 2],
-                                          float* __restrict__ qd) {
+                                          float* __restrict__ qd, int qd_rows) {
   float2 f[REC_RT / 2], q[REC_RT / 2];
   float v[REC_CT];
 #pragma unroll
@@ -95,9 +95,17 @@ __device__ __forceinline__ void rec_token(const float* __restrict__ row, int dkp
 #pragma unroll
     for (int a = 0; a < REC_RT / 2; ++a) cum[a] = make_float2(cum[a].x * f[a].x, cum[a].y * f[a].y);
     if (qd) {
+      if (qd_rows == REC_RT && (reinterpret_cast<uintptr_t>(qd) & 15) == 0) {
 #pragma unroll
-      for (int a = 0; a < REC_RT / 2; a += 2)
-        *reinterpret_cast<float4*>(qd + 2 * a) = make_float4(cum[a].x * q[a].x, cum[a].y * q[a].y, cum[a + 1].x * q[a + 1].x, cum[a + 1].y * q[a + 1].y);
+        for (int a = 0; a < REC_RT / 2; a += 2)
+          *reinterpret_cast<float4*>(qd + 2 * a) = make_float4(cum[a].x * q[a].x, cum[a].y * q[a].y, cum[a + 1].x * q[a + 1].x, cum[a + 1].y * q[a + 1].y);
+      } else {  // a slice that the head's rows end in, or rows that do not start on 16 bytes
+#pragma unroll
+        for (int a = 0; a < REC_RT / 2; ++a) {
+          if (2 * a < qd_rows) qd[2 * a] = cum[a].x * q[a].x;
+          if (2 * a + 1 < qd_rows) qd[2 * a + 1] = cum[a].y * q[a].y;
+        }
+      }
     }
   }
   *reinterpret_cast<float4*>(&v[0]) = *reinterpret_cast<const float4*>(row + 2 * dkp + jl);
@@ -147,6 +155,7 @@ hgrn2_scan_kernel(const float* __restrict__ g, float* __restrict__ state, const 
   // the correction's inputs are written once per head: by the first column group of the first column slice
   const bool corr = SEG && !from_state;
   float* qd_row = (corr && live && c == 0 && blockIdx.z == 0 && i0 < dk) ? qd + hd * dk + i0 : nullptr;
+  const int qd_rows = min(REC_RT, dk - i0);  // rows of this slice that the head has
   float2 cum[REC_RT / 2];
 #pragma unroll
   for (int a = 0; a < REC_RT / 2; ++a) cum[a] = make_float2(1.f, 1.f);
@@ -231,15 +240,15 @@ hgrn2_scan_kernel(const float* __restrict__ g, float* __restrict__ state, const 
       float a0[REC_CT], a1[REC_CT], a2[REC_CT], a3[REC_CT];
       float* qdt = qd_row ? qd_row + (size_t)(cs + tt) * HK : nullptr;
       if (corr) {
-        rec_token<true>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, qdt);
-        rec_token<true>(cur + (tt + 1) * rowlen, dkp, i0, jl, S, a1, cum, qdt ? qdt + HK : nullptr);
-        rec_token<true>(cur + (tt + 2) * rowlen, dkp, i0, jl, S, a2, cum, qdt ? qdt + 2 * HK : nullptr);
-        rec_token<true>(cur + (tt + 3) * rowlen, dkp, i0, jl, S, a3, cum, qdt ? qdt + 3 * HK : nullptr);
+        rec_token<true>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, qdt, qd_rows);
+        rec_token<true>(cur + (tt + 1) * rowlen, dkp, i0, jl, S, a1, cum, qdt ? qdt + HK : nullptr, qd_rows);
+        rec_token<true>(cur + (tt + 2) * rowlen, dkp, i0, jl, S, a2, cum, qdt ? qdt + 2 * HK : nullptr, qd_rows);
+        rec_token<true>(cur + (tt + 3) * rowlen, dkp, i0, jl, S, a3, cum, qdt ? qdt + 3 * HK : nullptr, qd_rows);
       } else {
-        rec_token<false>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, nullptr);
-        rec_token<false>(cur + (tt + 1) * rowlen, dkp, i0, jl, S, a1, cum, nullptr);
-        rec_token<false>(cur + (tt + 2) * rowlen, dkp, i0, jl, S, a2, cum, nullptr);
-        rec_token<false>(cur + (tt + 3) * rowlen, dkp, i0, jl, S, a3, cum, nullptr);
+        rec_token<false>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, nullptr, 0);
+        rec_token<false>(cur + (tt + 1) * rowlen, dkp, i0, jl, S, a1, cum, nullptr, 0);
+        rec_token<false>(cur + (tt + 2) * rowlen, dkp, i0, jl, S, a2, cum, nullptr, 0);
+        rec_token<false>(cur + (tt + 3) * rowlen, dkp, i0, jl, S, a3, cum, nullptr, 0);
       }
       emit(cs + tt, a0);
       emit(cs + tt + 1, a1);
@@ -248,8 +257,8 @@ hgrn2_scan_kernel(const float* __restrict__ g, float* __restrict__ state, const 
     }
     for (; tt < cnt; ++tt) {
       float a0[REC_CT];
-      if (corr) rec_token<true>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, qd_row ? qd_row + (size_t)(cs + tt) * HK : nullptr);
-      else rec_token<false>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, nullptr);
+      if (corr) rec_token<true>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, qd_row ? qd_row + (size_t)(cs + tt) * HK : nullptr, qd_rows);
+      else rec_token<false>(cur + tt * rowlen, dkp, i0, jl, S, a0, cum, nullptr, 0);
       emit(cs + tt, a0);
     }
     cp_async_wait_all();
@@ -285,7 +294,9 @@ __global__ void hgrn2_chain_kernel(const int* __restrict__ segs, int n_seg, floa
   const int r = segs[4 * b];
   const size_t per = (size_t)dk * dv;
   float* S_g = state + ((size_t)slot_ids[r] * H + hd) * per;
-  for (int e = threadIdx.x; e < dk * dv; e += blockDim.x) {
+  {  // one state entry per thread: the chain's steps are dependent, its entries are not
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= dk * dv) return;
     const int i = e / dv;
     float t = seg_state[((size_t)b * H + hd) * per + e];
     for (int k = b + 1; k < n_seg && segs[4 * k] == r && !(segs[4 * k + 3] & 1); ++k) {
@@ -404,7 +415,7 @@ JLX_API int jlx_hgrn2_scan(const float* qfv, int splits, long long split_stride,
 #undef REC_GO
   JLX_LAUNCH_CHECK("hgrn2_scan");
   if (segs) {
-    hgrn2_chain_kernel<<<dim3(n_seg, H), 256, 0, stream>>>(segs, n_seg, seg_state, seg_decay, state, slot_ids, H, dk, dv);
+    hgrn2_chain_kernel<<<dim3(n_seg, H, (dk * dv + 255) / 256), 256, 0, stream>>>(segs, n_seg, seg_state, seg_decay, state, slot_ids, H, dk, dv);
     JLX_LAUNCH_CHECK("hgrn2_chain");
     const int tiles = (seg_tokens + COR_TOK - 1) / COR_TOK;
     const size_t csm = sizeof(float) * ((size_t)dk * COR_COL + (size_t)COR_TOK * (dk + 1));

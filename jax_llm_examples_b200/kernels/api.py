@@ -264,36 +264,66 @@ def short_conv(h32: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | No
 
 
 # ------------------------------------------------------------------------------- recurrences
-def hgrn2_scan_scratch(n_tokens: int, heads: int, dk: int, dv: int) -> int:
-    """float32 elements of scratch that ``hgrn2_scan`` needs: the gated rows and the un-normed outputs."""
-    return -(-n_tokens * heads * (2 * dk + dv) // 4) * 4 + n_tokens * heads * dv
+def _up4(n: int) -> int:
+    return -(-n // 4) * 4
+
+
+def hgrn2_scan_scratch(n_tokens: int, heads: int, dk: int, dv: int, n_segments: int = 0) -> int:
+    """float32 elements of scratch that ``hgrn2_scan`` needs: the gated rows and the un-normed outputs, and with
+    segments their end/start states, the products of their gates, and the outputs' correction inputs."""
+    n = _up4(n_tokens * heads * (2 * dk + dv)) + _up4(n_tokens * heads * dv)
+    if n_segments:
+        n += _up4(n_segments * heads * dk * dv) + _up4(n_segments * heads * dk) + _up4(n_tokens * heads * dk)
+    return n
 
 
 def hgrn2_scan(qfv: torch.Tensor, splits: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                cu_q: torch.Tensor, slot_ids: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, out: torch.Tensor,
-               heads: int, dk: int, dv: int, scratch: torch.Tensor | None = None) -> None:
+               heads: int, dk: int, dv: int, scratch: torch.Tensor | None = None, segments: torch.Tensor | None = None,
+               n_segments: int = 0, segment_tokens: int = 0) -> None:
     """The gated recurrence S = diag(f) S + (1 - f) v^T, o = S^T silu(q) over each request's tokens, then the per-head
     RMS norm of o (three launches: gates, scan, norm).  qfv: float32 [N, 2 H dk + H dv] = [q | f | v] before their
     activations (or ``splits`` partials); state: float32 [slots, H, dk, dv]; out: [N, H dv]; scratch: float32 of
-    ``hgrn2_scan_scratch`` elements (made here if not given)."""
-    _contig(qfv, f_bias, lower, state, norm_weight, out, scratch)
+    ``hgrn2_scan_scratch`` elements (made here if not given).
+    ``segments`` (int32 [n_segments, 4] = request, first row, end row, flags; at most ``segment_tokens`` rows each, every
+    token in exactly one, a request's segments in order): long portions are scanned as several segments at once, each but
+    a request's first from a zero state; two more kernels chain the segments' states and correct their outputs.  flags:
+    1 = the request's first segment, 2 = the request has several."""
+    _contig(qfv, f_bias, lower, state, norm_weight, out, scratch, segments)
     if any(t.dtype != torch.float32 for t in (qfv, f_bias, lower, state)) or (norm_weight is not None and norm_weight.dtype != torch.float32):
         raise KernelError("hgrn2_scan: projections, gate constants, state and norm weight must be float32")
     if tuple(state.shape[1:]) != (heads, dk, dv) or out.shape[1] != heads * dv:
         raise KernelError(f"hgrn2_scan: shapes do not fit: state {tuple(state.shape)}, out {tuple(out.shape)}")
     N = out.shape[0]
-    need = hgrn2_scan_scratch(N, heads, dk, dv)
+    if segments is None:
+        n_segments = 0
+    elif segments.dtype != torch.int32 or segments.numel() < 4 * n_segments or n_segments <= 0 or segment_tokens <= 0:
+        raise KernelError("hgrn2_scan: segments must be int32 [n_segments, 4] with a positive segment size")
+    need = hgrn2_scan_scratch(N, heads, dk, dv, n_segments)
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=out.device)
     if scratch.dtype != torch.float32 or scratch.numel() < need or scratch.data_ptr() % 16:
         raise KernelError("hgrn2_scan: scratch must be float32, 16-byte aligned, with hgrn2_scan_scratch() elements")
-    gates, o32 = scratch, scratch[need - N * heads * dv:]
+    at = 0
+
+    def cut(n: int):
+        nonlocal at
+        v = scratch[at:at + n]
+        at += _up4(n)
+        return v
+
+    gates, o32 = cut(N * heads * (2 * dk + dv)), cut(N * heads * dv)
+    seg_state = seg_decay = qd = None
+    if n_segments:
+        seg_state, seg_decay, qd = cut(n_segments * heads * dk * dv), cut(n_segments * heads * dk), cut(N * heads * dk)
     sp, stride = _splits(qfv, splits)
     global _launches
     _run("recurrent", "jlx_hgrn2_scan", _ptr(qfv), c_int(sp), c_longlong(stride), _ptr(f_bias), _ptr(lower), _ptr(state),
          _ptr(cu_q), _ptr(slot_ids), _ptr(norm_weight), c_float(eps), _ptr(gates), _ptr(o32), _ptr(out), c_int(code(out.dtype)),
-         c_int(N), c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), c_int(sm_count()), _stream())
-    _launches += 2  # the gates, the scan and the norm
+         c_int(N), c_int(slot_ids.numel()), c_int(heads), c_int(dk), c_int(dv), c_int(sm_count()),
+         _ptr(segments) if n_segments else None, c_int(n_segments), c_int(segment_tokens), _ptr(seg_state), _ptr(seg_decay),
+         _ptr(qd), _stream())
+    _launches += 2 + (2 if n_segments else 0)  # gates, scan, (chain, correction,) norm
 
 
 # -------------------------------------------------------------------------- latent attention

@@ -4,9 +4,11 @@ from __future__ import annotations
 
 import torch
 
+import numpy as np
+
 from ..kernels import api as K
 from ..tracing import scope
-from .base import LayerCache, Mixer, StateNeed, StepContext, as_rows, register_part
+from .base import LayerCache, Mixer, StateNeed, StepContext, StepShape, as_rows, register_part
 from .conv import ResidualShortConv
 from .linear import linear
 
@@ -38,6 +40,28 @@ class InputConvMixer(Mixer):
         return self.input_conv.forward(ctx, h32, states[0]), states[1:]
 
 
+SEGMENT_TOKENS = 256  # tokens of a long portion that one block of the recurrence kernel walks
+
+
+def plan_scan_segments(shape: StepShape) -> dict:
+    """The step planner of the recurrences: when a request brings a long portion (at least two segments), the step's
+    tokens cut into segments of SEGMENT_TOKENS, int32 [n, 4] = (request, first row, end row, flags: 1 = the request's
+    first segment, 2 = the request has several).  A recurrence over time gives the GPU only its state's parallelism;
+    segments scanned at once from a zero state, and corrected afterwards, multiply it by their number.  Steps of short
+    portions and single tokens get no list (their tokens are walked in order, one block per request and head)."""
+    if max(shape.q_lens) < 2 * SEGMENT_TOKENS:
+        return {}
+    segs, n0 = [], 0
+    for r, T in enumerate(shape.q_lens):
+        if T >= 2 * SEGMENT_TOKENS:
+            for c in range(0, T, SEGMENT_TOKENS):
+                segs.append((r, n0 + c, n0 + min(T, c + SEGMENT_TOKENS), (1 if c == 0 else 0) | 2))
+        else:
+            segs.append((r, n0, n0 + T, 1))
+        n0 += T
+    return {"scan_segments": np.array(segs, dtype=np.int32).reshape(-1, 4)}
+
+
 class HGRN2(InputConvMixer):
     """Gated linear recurrence with a matrix state per head, in which the forget gate also decides what is written
     (there is no key):  q = silu(W_q h), v = W_v h, f = lower + (1 - lower) * sigmoid(W_f h + b_f);
@@ -63,16 +87,21 @@ class HGRN2(InputConvMixer):
     def own_state_needs(self):
         return (StateNeed((self.heads, self.dim, self.vdim), torch.float32),)
 
+    def step_planners(self):
+        return (plan_scan_segments,)
+
     def forward(self, ctx: StepContext, h, cache: LayerCache, h32: torch.Tensor | None = None):
         a, (state,) = self.read_input(ctx, h32, cache)
         with scope("qkv_matmul"):
             qfv = as_rows(linear(ctx, a, self.w_qfv, torch.float32, partials=True))
         o = torch.empty((a.shape[0], self.heads * self.vdim), dtype=ctx.runtime.dtype, device=a.device)
         with scope("attention"):
-            need = K.hgrn2_scan_scratch(a.shape[0], self.heads, self.dim, self.vdim)
+            segs = ctx.arrays.get("scan_segments")
+            n_seg = 0 if segs is None else segs.numel() // 4
+            need = K.hgrn2_scan_scratch(a.shape[0], self.heads, self.dim, self.vdim, n_seg)
             scratch = ctx.workspace.get("hgrn2_scan", need, torch.float32) if ctx.workspace else None
             K.hgrn2_scan(qfv.data, qfv.splits, self.f_bias, self.lower, state, ctx.cu_q, ctx.slot_ids, self.norm_weight,
-                         self.eps, o, self.heads, self.dim, self.vdim, scratch)
+                         self.eps, o, self.heads, self.dim, self.vdim, scratch, segs if n_seg else None, n_seg, SEGMENT_TOKENS)
         with scope("projection"):
             return linear(ctx, o, self.w_o, torch.float32, partials=True)
 

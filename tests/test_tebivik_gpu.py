@@ -152,6 +152,50 @@ def test_hgrn2_part_in_portions_and_token_by_token(name, dtype, tol, H_, dk, dv,
         _close(torch.cat(got[r]), ref[r], tol, f"{name} request {r}")
 
 
+@pytest.mark.parametrize("name, dtype, tol", DTYPES)
+def test_hgrn2_long_portions_are_scanned_in_segments(name, dtype, tol):
+    """Portions of at least two segments are scanned segment by segment at once (each but the first from a zero state,
+    then chained and corrected): a request of 700 tokens beside a short one and one that decodes, then a second long
+    portion that goes on from the carried state, against the plain recurrence over the whole sequences; and against the
+    same tokens walked in order (no segments), to within rounding."""
+    from jax_llm_examples_b200.parts import HGRN2, LayerCache, Runtime
+    from jax_llm_examples_b200.parts.recurrent import SEGMENT_TOKENS, plan_scan_segments
+
+    torch.manual_seed(3)
+    H_, dk, dv, D = 3, 12, 20, 32
+    rt = Runtime(dtype, torch.device(DEV))
+    wd = {k: v.to(dtype) for k, v in _hgrn2_weights(D, H_, dk, dv).items()}
+    wd["lower"] = (0.05 + 0.9 * torch.rand(H_ * dk)).to(dtype)
+    mixer = HGRN2(torch.cat([wd["q"], wd["f"], wd["v"]]).to(DEV), wd["f.b"].to(DEV), wd["lower"].to(DEV), wd["norm"].to(DEV),
+                  wd["o"].to(DEV), H_, dk, dv, 1e-5)
+    assert mixer.step_planners() == (plan_scan_segments,)
+    lens = (2 * SEGMENT_TOKENS + 188 + 2 * SEGMENT_TOKENS + 5, 40, 9)
+    seqs = [torch.randn(n, D).to(dtype) for n in lens]
+    ref = [plain.hgrn2(s.double(), {"m." + k: v.double() for k, v in wd.items()}, "m.", {"heads": H_, "dim": dk, "vdim": dv}, 1e-5)
+           for s in seqs]
+    first = 2 * SEGMENT_TOKENS + 188
+    steps = [[(0, 0, first), (1, 0, 40), (2, 0, 1)], [(2, 1, 2), (0, first, lens[0])], [(2, 2, 9)]]
+    results = {}
+    for planned in (True, False):
+        state = torch.zeros(3, H_, dk, dv, device=DEV)
+        got = [[], [], []]
+        for step in steps:
+            h = torch.cat([seqs[r][lo:hi] for r, lo, hi in step]).float().to(DEV)
+            ctx = _ctx(rt, [hi - lo for _, lo, hi in step], [lo for _, lo, _ in step], [r for r, _, _ in step],
+                       planners=mixer.step_planners() if planned else ())
+            assert ("scan_segments" in ctx.arrays) == (planned and max(hi - lo for _, lo, hi in step) >= 2 * SEGMENT_TOKENS)
+            out = H.as_rows_sum(mixer.forward(ctx, None, LayerCache(None, None, False, state, (state,)), h32=h))
+            o = 0
+            for r, lo, hi in step:
+                got[r].append(out[o:o + hi - lo])
+                o += hi - lo
+        results[planned] = [torch.cat(g) for g in got]
+        for r in range(3):
+            _close(results[planned][r], ref[r], tol, f"{name} request {r} segments={planned}")
+    for r in range(3):
+        _close(results[True][r], results[False][r], 1e-5 if dtype == torch.float32 else 2e-2, f"{name} request {r}: segments against in order")
+
+
 def _latent_weights(D, m):
     H_, dn, dr, dv, qr, kr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
     g = lambda *s: torch.randn(*s) * 0.3
@@ -361,6 +405,36 @@ def test_long_decoding_and_a_far_token(folders):
         engine = _engine(folders[name], dtype, max_tokens=320)
         got, _ = H.run_trace(engine, H.trace_tail_decode({"a": toks}, tail=300), record_routing=False)
         TH.compare(folders[name], {"a": toks}, got, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_whole_and_in_portions(folders, dtype):
+    """560 tokens in one step (the recurrences scan it in segments; attention sees keys 500 tokens back), the same in two
+    portions that are walked in order, and beside a short request: against the plain implementation at places near
+    the start, around the segments' edges and at the end, and against each other."""
+    import jax_llm_examples_b200 as J
+
+    name = "small"
+    vocab = TH.config(name)["vocab"]
+    rng = random.Random(5)
+    toks, other = [rng.randrange(vocab) for _ in range(560)], [rng.randrange(vocab) for _ in range(30)]
+    want = [0, 1, 2, 254, 255, 256, 257, 300, 511, 512, 513, 558, 559]
+    engine = _engine(folders[name], dtype, max_tokens=1024)
+    a, b = engine.new_request(), engine.new_request()
+    whole = engine.step([J.StepEntry(a, toks, want), J.StepEntry(b, other, [29])]).cpu().numpy().copy()
+    engine.finish(a), engine.finish(b)
+    a = engine.new_request()
+    first = engine.step([J.StepEntry(a, toks[:300], [w for w in want if w < 300])]).cpu().numpy().copy()
+    second = engine.step([J.StepEntry(a, toks[300:], [w - 300 for w in want if w >= 300])]).cpu().numpy().copy()
+    engine.check_status()
+    engine.finish(a)
+    parts = np.concatenate([first, second])
+    ref = TH.plain_logits(folders[name], toks)
+    for k, w in enumerate(want):
+        assert TH.row_err(whole[k], ref[w]) < TH.TOL[dtype], f"{dtype}: position {w} of the whole prompt"
+        assert TH.row_err(parts[k], ref[w]) < TH.TOL[dtype], f"{dtype}: position {w} of the prompt in portions"
+        assert TH.row_err(whole[k], parts[k]) < (1e-5 if dtype == "float32" else TH.TOL[dtype])
+    assert TH.row_err(whole[len(want)], TH.plain_logits(folders[name], other)[29]) < TH.TOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
