@@ -362,8 +362,10 @@ JLX_API int jlx_attention_latent(const float* q_lat, const float* q_rot, const v
   const bool big = rank > 512;             // latents above 512: two heads per warp, else four
   const int hpw = big ? 2 : 4;
   const int groups = (H + hpw - 1) / hpw;  // warps' worth of heads
-  const int nwarp = groups < LAT_WARPS ? groups : LAT_WARPS;
-  const size_t smem = sizeof(float) * ((size_t)nwarp * hpw * dk + (size_t)LAT_TILE * ldk);
+  int nwarp = groups < LAT_WARPS ? groups : LAT_WARPS;
+  auto smem_for = [&](int warps) { return sizeof(float) * ((size_t)warps * hpw * dk + (size_t)LAT_TILE * ldk); };
+  while (nwarp > 1 && smem_for(nwarp) > 200 * 1024) nwarp >>= 1;  // fewer heads per block where the rows are long
+  const size_t smem = smem_for(nwarp);
   JLX_REQUIRE(smem <= 200 * 1024, "attention_latent: a key tile of %d x %d does not fit into shared memory", LAT_TILE, dk);
   const int hb = (groups + nwarp - 1) / nwarp;
   JLX_REQUIRE(hb <= 65535 && H <= 65535, "attention_latent: too many heads (%d)", H);

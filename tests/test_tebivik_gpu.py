@@ -319,12 +319,13 @@ def test_prompt_softmax_stops_at_the_causal_edge_and_counts_the_sink_once(T, L, 
 
 
 @pytest.mark.parametrize("name, dtype, tol", DTYPES)
-def test_biased_mlp_and_reinjection_block(name, dtype, tol):
+@pytest.mark.parametrize("D, F", [(40, 72), (38, 70)])  # four values per access, and one
+def test_biased_mlp_and_reinjection_block(name, dtype, tol, D, F):
     from jax_llm_examples_b200.parts import DenseBiasedMLP, ReinjectionBlock, Rows, Runtime
 
     torch.manual_seed(1)
     rt = Runtime(dtype, torch.device(DEV))
-    D, F, N = 40, 72, 6
+    N = 6
     w = {"up": torch.randn(F, D) * 0.3, "up.b": torch.randn(F) * 0.5, "down": torch.randn(D, F) * 0.3, "down.b": torch.randn(D)}
     wd = {k: v.to(dtype) for k, v in w.items()}
     ff = DenseBiasedMLP(wd["up"].to(DEV), wd["up.b"].to(DEV), wd["down"].to(DEV), wd["down.b"].to(DEV), "relu2")
