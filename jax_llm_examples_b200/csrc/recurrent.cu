@@ -1,6 +1,6 @@
 // Gated linear recurrences with a matrix state per head, in 32-bit, over the flattened batch of a step.
 //
-// HGRN2 form (the forget gate also says how much is written; there is no key):
+// HGRN2 form (the forget gate f is also the write gate 1 - f; keys do not exist):
 //   f_t = lower + (1 - lower) * sigmoid(f_pre_t + f_bias)            per head and channel i < dk
 //   S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T                         S: [dk, dv] per request and head
 //   o_t = S_t^T silu(q_pre_t)

@@ -10,7 +10,7 @@ from .base import Part, StateNeed, StepContext, register_part
 
 class ResidualShortConv(Part):
     """h <- h + conv(h): a causal convolution on each channel alone, ``weight`` [D, taps], no bias:
-    conv(h)_t = sum_j weight[:, j] * h_(t - taps + 1 + j), zeros before the sequence's start.  The last taps - 1
+    conv(h)_t = sum_j weight[:, j] * h_(t - taps + 1 + j), with h = 0 at negative times.  The last taps - 1
     inputs of a request are its state (float32), so a sequence may come in portions of any size.  Input and sums are
     float32; the output has the activations' type."""
 

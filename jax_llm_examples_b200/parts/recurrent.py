@@ -63,8 +63,8 @@ def plan_scan_segments(shape: StepShape) -> dict:
 
 
 class HGRN2(InputConvMixer):
-    """Gated linear recurrence with a matrix state per head, in which the forget gate also decides what is written
-    (there is no key):  q = silu(W_q h), v = W_v h, f = lower + (1 - lower) * sigmoid(W_f h + b_f);
+    """Gated linear recurrence with a matrix state per head, whose forget gate f doubles as the write gate 1 - f
+    (keys do not exist in this form):  q = silu(W_q h), v = W_v h, f = lower + (1 - lower) * sigmoid(W_f h + b_f);
     S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T;  o_t = S_t^T q_t;  each head's o is RMS-normed over its value size with
     one weight shared by the heads, and the heads go through W_o.  Gates, state and norm are float32.
 

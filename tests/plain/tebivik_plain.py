@@ -52,7 +52,7 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def causal_conv(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """h: [T, D]; w: [D, taps].  y_t = sum_j w[:, j] * h_(t - taps + 1 + j), zeros before the sequence's start."""
+    """h: [T, D]; w: [D, taps].  y_t = sum_j w[:, j] * h_(t - taps + 1 + j), h = 0 at negative times."""
     T, taps = h.shape[0], w.shape[1]
     y = torch.zeros_like(h)
     for t in range(T):
@@ -69,7 +69,7 @@ def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
 
 def rotate_pairs(x: torch.Tensor, positions: torch.Tensor, base: float, dims: int) -> torch.Tensor:
     """x: [T, ..., d].  The first ``dims`` entries of the last axis are rotated in pairs (2i, 2i+1) by the angle
-    position * base^(-2i/dims); the rest pass unchanged."""
+    position * base^(-2i/dims); entries from ``dims`` on are copied."""
     i = torch.arange(dims // 2, dtype=torch.float64)
     freq = base ** (-2.0 * i / dims)
     ang = positions.to(torch.float64)[:, None] * freq[None, :]  # [T, dims/2]
@@ -103,7 +103,7 @@ def hgrn2(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor
 
 def latent_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
     """Attention whose queries, keys and values come out of low-rank latents; one rotated key part is shared by
-    all heads; the softmax's denominator holds one more term exp(sink_h) that has no key and no value."""
+    all heads; the softmax's denominator holds one more term exp(sink_h) to which no key and no value row belong."""
     H, dn, dr, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     T = h.shape[0]
     pos = torch.arange(T)
