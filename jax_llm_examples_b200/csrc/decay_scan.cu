@@ -1,0 +1,292 @@
+// Linear attention with a decay per key channel: a matrix state S [dk, dv] per request and head that every token
+// decays row by row and adds an outer product to,
+//
+//     S_t = diag(d_t) S_(t-1) + k_t v_t^T,
+//
+// read either AFTER the update,  o_t = S_t^T q_t  (gated linear attention), or BEFORE it with a bonus u for the
+// token itself,  o_t = (S_(t-1) + diag(u) k_t v_t^T)^T q_t  (RWKV-style time mixing).  Everything here is 32-bit:
+// decays, their logarithms and exponentials, the state, the sums.  The kernels:
+//
+//   token_shift_blend  rows m of [M, N, D]: h + (h_prev - h) * mu_m, h_prev the request's previous token (its state
+//                      [D] across steps, zeros at the start); the step's last h of a request becomes its state.
+//   decay_prep         q (scaled), k, v and the decay d of every token and head from projected rows (split-K partials
+//                      are added on the way); d = exp(-exp(z + b)) or sigmoid(z + b)^(1/tau).
+//   decay_scan         the recurrence over each request's tokens, in order; the state lives in registers.
+//   head_norm_gate     each head's o divided by its root mean square, times a weight, times silu(gate), times a
+//                      constant, written into (a column range of) the rows that the output product reads.
+//
+// Every sum runs in an order that depends on the token alone, so a token's result does not change with the batch or
+// with how its prompt was cut into steps.
+#include "common.cuh"
+
+// Projected rows that may still be split-K partials: element (row, col) = sum_z p[z * split_stride + row * ld + col].
+struct RowsView {
+  const float* p;
+  long long split_stride;
+  long long ld;
+  int splits;
+  int pad_;
+};
+
+__device__ __forceinline__ float rows_at(const RowsView& v, size_t row, int col) {
+  float s = 0.f;
+  for (int z = 0; z < v.splits; ++z) s += v.p[(size_t)z * v.split_stride + row * v.ld + col];
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------------ token shift
+// Blocks [0, R): request r's first token of the step and the move of its state (one thread per channel reads the old
+// state and then writes the new one).  Blocks [R, R + N): every other token; they never touch the state.
+template <typename T>
+__global__ void token_shift_blend_kernel(const float* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
+                                         const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
+                                         const int* __restrict__ req_of_token, T* __restrict__ out, int N, int R, int D, int M) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  int n;
+  const float* prev;
+  float* st = nullptr;
+  int last = 0;
+  if ((int)blockIdx.x < R) {
+    const int r = blockIdx.x;
+    n = cu_q[r];
+    last = cu_q[r + 1] - 1;
+    if (last < n) return;
+    st = state + (size_t)slot_ids[r] * D;
+    prev = st;
+  } else {
+    n = blockIdx.x - R;
+    if (n == cu_q[req_of_token[n]]) return;  // a first token: served by its request's block
+    prev = h + (size_t)(n - 1) * D;
+  }
+  const float* cur = h + (size_t)n * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float c = cur[d], p = prev[d];
+    const float diff = p - c;
+    for (int m = 0; m < M; ++m) out[((size_t)m * N + n) * D + d] = from_f32<T>(fmaf(diff, mu[(size_t)m * D + d], c));
+    if (st) st[d] = h[(size_t)last * D + d];
+  }
+}
+
+JLX_API int jlx_token_shift_blend(const float* h, const float* mu, float* state, const int* cu_q, const int* slot_ids,
+                                  const int* req_of_token, void* out, int out_dtype, int N, int R, int D, int M,
+                                  cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && R >= 0 && D > 0 && M >= 1, "token_shift_blend: bad sizes N=%d R=%d D=%d M=%d", N, R, D, M);
+  if (N == 0) return 0;
+  const int threads = D >= 1024 ? 256 : 128;
+  JLX_DISPATCH_DTYPE(out_dtype, T, {
+    JLX_CUDA(jlx_launch_pdl(token_shift_blend_kernel<T>, dim3(R + N), dim3(threads), 0, stream, h, mu, state, cu_q, slot_ids,
+                            req_of_token, (T*)out, N, R, D, M));
+  });
+  JLX_LAUNCH_CHECK("token_shift_blend");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ decay prep
+enum { DECAY_DOUBLE_EXP = 0, DECAY_SIGMOID_POWER = 1 };
+
+// One block per (token, head).
+__global__ void decay_prep_kernel(RowsView q, RowsView k, RowsView v, RowsView z, const float* __restrict__ z_bias, int mode,
+                                  float inv_tau, float q_scale, float* __restrict__ qo, float* __restrict__ ko,
+                                  float* __restrict__ d_out, float* __restrict__ vo, int H, int dk, int dv) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t n = blockIdx.x;
+  const int hd = blockIdx.y;
+  const size_t at_k = (n * H + hd) * dk, at_v = (n * H + hd) * dv;
+  for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+    const int c = hd * dk + i;
+    qo[at_k + i] = rows_at(q, n, c) * q_scale;
+    ko[at_k + i] = rows_at(k, n, c);
+    const float x = rows_at(z, n, c) + (z_bias ? z_bias[c] : 0.f);
+    float d;
+    if (mode == DECAY_DOUBLE_EXP) {
+      d = expf(-expf(x));
+    } else {
+      // sigmoid(x)^(1/tau) = exp(-softplus(-x) / tau), softplus(y) = max(y, 0) + log1p(exp(-|y|))
+      const float sp = fmaxf(-x, 0.f) + log1pf(expf(-fabsf(x)));
+      d = expf(-sp * inv_tau);
+    }
+    d_out[at_k + i] = d;
+  }
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) vo[at_v + j] = rows_at(v, n, hd * dv + j);
+}
+
+JLX_API int jlx_decay_prep(const RowsView* q, const RowsView* k, const RowsView* v, const RowsView* z, const float* z_bias,
+                           int mode, float tau, float q_scale, float* qo, float* ko, float* d_out, float* vo, int N, int H,
+                           int dk, int dv, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && H > 0 && dk > 0 && dv > 0 && H <= 65535, "decay_prep: bad sizes N=%d H=%d dk=%d dv=%d", N, H, dk, dv);
+  JLX_REQUIRE(mode == DECAY_DOUBLE_EXP || (mode == DECAY_SIGMOID_POWER && tau > 0.f), "decay_prep: unknown decay form or tau <= 0");
+  if (N == 0) return 0;
+  JLX_CUDA(jlx_launch_pdl(decay_prep_kernel, dim3(N, H), dim3(dk + dv >= 256 ? 128 : 64), 0, stream, *q, *k, *v, *z, z_bias, mode,
+                          mode == DECAY_SIGMOID_POWER ? 1.f / tau : 0.f, q_scale, qo, ko, d_out, vo, H, dk, dv));
+  JLX_LAUNCH_CHECK("decay_prep");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ the recurrence
+// One block per (request, head, slice of 32 value columns).  Lane = a value column; warp w keeps rows [w NR, (w+1) NR)
+// of S for that column in registers.  The tokens' q, k, d rows and v slice come through shared memory SCAN_TB tokens
+// at a time; between two barriers a warp walks those tokens (o does not feed back into S) and leaves its part of each
+// o; the parts are added in warp order.
+#define SCAN_TB 16
+
+template <int NR, bool READ_AFTER>
+__global__ void decay_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ d,
+                                  const float* __restrict__ v, const float* __restrict__ u, float* __restrict__ state,
+                                  const int* __restrict__ cu_q, const int* __restrict__ slot_ids, float* __restrict__ o,
+                                  int H, int dk, int dv) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int dkp = W * NR;
+  float* qs = smem;                  // [SCAN_TB][dkp]
+  float* ks = qs + SCAN_TB * dkp;
+  float* ds = ks + SCAN_TB * dkp;
+  float* vs = ds + SCAN_TB * dkp;    // [SCAN_TB][32]
+  float* part = vs + SCAN_TB * 32;   // [SCAN_TB][W][32]
+  const int r = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * 32;
+  const int j = j0 + lane;
+  const bool col = j < dv;
+  const int i0 = warp * NR;
+  float uu[NR];
+#pragma unroll
+  for (int ii = 0; ii < NR; ++ii) uu[ii] = (!READ_AFTER && u && i0 + ii < dk) ? u[hd * dk + i0 + ii] : 0.f;
+  pdl_wait();
+  const int n0 = cu_q[r], n1 = cu_q[r + 1];
+  if (n1 <= n0) return;
+  float* S = state + ((size_t)slot_ids[r] * H + hd) * dk * dv;
+  float s[NR];
+#pragma unroll
+  for (int ii = 0; ii < NR; ++ii) s[ii] = (col && i0 + ii < dk) ? S[(size_t)(i0 + ii) * dv + j] : 0.f;
+
+  auto stage = [&](int t0) {
+    const int cnt = min(SCAN_TB, n1 - t0);
+    for (int idx = threadIdx.x; idx < cnt * dkp; idx += blockDim.x) {
+      const int tt = idx / dkp, i = idx - tt * dkp;
+      const size_t at = ((size_t)(t0 + tt) * H + hd) * dk + i;
+      const bool in = i < dk;
+      qs[idx] = in ? q[at] : 0.f;
+      ks[idx] = in ? k[at] : 0.f;
+      ds[idx] = in ? d[at] : 1.f;
+    }
+    for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
+      const int tt = idx >> 5, l = idx & 31;
+      vs[idx] = j0 + l < dv ? v[((size_t)(t0 + tt) * H + hd) * dv + j0 + l] : 0.f;
+    }
+  };
+
+  stage(n0);
+  for (int t0 = n0; t0 < n1; t0 += SCAN_TB) {
+    const int cnt = min(SCAN_TB, n1 - t0);
+    __syncthreads();  // the staged tokens are there; the parts of the tokens before are consumed
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float vj = vs[tt * 32 + lane];
+      const float* qt = qs + tt * dkp + i0;
+      const float* kt = ks + tt * dkp + i0;
+      const float* dt = ds + tt * dkp + i0;
+      float acc = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < NR; ++ii) {
+        const float kv = kt[ii] * vj;
+        if (READ_AFTER) {
+          s[ii] = fmaf(dt[ii], s[ii], kv);
+          acc = fmaf(qt[ii], s[ii], acc);
+        } else {
+          acc = fmaf(qt[ii], fmaf(uu[ii], kv, s[ii]), acc);
+          s[ii] = fmaf(dt[ii], s[ii], kv);
+        }
+      }
+      part[(tt * W + warp) * 32 + lane] = acc;
+    }
+    __syncthreads();  // the parts are there; the staged tokens are consumed
+    for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
+      const int tt = idx >> 5, l = idx & 31;
+      float sum = 0.f;
+      for (int w = 0; w < W; ++w) sum += part[(tt * W + w) * 32 + l];
+      if (j0 + l < dv) o[((size_t)(t0 + tt) * H + hd) * dv + j0 + l] = sum;
+    }
+    if (t0 + SCAN_TB < n1) stage(t0 + SCAN_TB);
+  }
+#pragma unroll
+  for (int ii = 0; ii < NR; ++ii)
+    if (col && i0 + ii < dk) S[(size_t)(i0 + ii) * dv + j] = s[ii];
+}
+
+template <int NR, bool READ_AFTER>
+static int launch_decay_scan(const float* q, const float* k, const float* d, const float* v, const float* u, float* state,
+                             const int* cu_q, const int* slot_ids, float* o, int R, int H, int dk, int dv, cudaStream_t stream) {
+  const int W = (dk + NR - 1) / NR;
+  const size_t smem = sizeof(float) * ((size_t)3 * SCAN_TB * W * NR + SCAN_TB * 32 + (size_t)SCAN_TB * W * 32);
+  if (smem > 48 * 1024)
+    JLX_CUDA(cudaFuncSetAttribute(decay_scan_kernel<NR, READ_AFTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  JLX_CUDA(jlx_launch_pdl(decay_scan_kernel<NR, READ_AFTER>, dim3(R, H, (dv + 31) / 32), dim3(W * 32), smem, stream, q, k, d, v, u,
+                          state, cu_q, slot_ids, o, H, dk, dv));
+  JLX_LAUNCH_CHECK("decay_scan");
+  return 0;
+}
+
+// q, k, d: float32 [N, H, dk]; v: [N, H, dv]; u: [H, dk] or null (only read before the update); state: [slots, H, dk, dv];
+// o: [N, H, dv].  read_after: 1 = o_t = S_t^T q_t;  0 = o_t = (S_(t-1) + diag(u) k_t v_t^T)^T q_t.
+JLX_API int jlx_decay_scan(const float* q, const float* k, const float* d, const float* v, const float* u, float* state,
+                           const int* cu_q, const int* slot_ids, float* o, int R, int H, int dk, int dv, int read_after,
+                           cudaStream_t stream) {
+  JLX_REQUIRE(R >= 0 && H > 0 && dk > 0 && dv > 0, "decay_scan: bad sizes R=%d H=%d dk=%d dv=%d", R, H, dk, dv);
+  JLX_REQUIRE(dk <= 512, "decay_scan: %d key channels per head; up to 512 are supported", dk);
+  JLX_REQUIRE(H <= 65535 && (dv + 31) / 32 <= 65535, "decay_scan: too many heads or value columns");
+  if (R == 0) return 0;
+#define JLX_SCAN(NR)                                                                                                      \
+  return read_after ? launch_decay_scan<NR, true>(q, k, d, v, u, state, cu_q, slot_ids, o, R, H, dk, dv, stream)          \
+                    : launch_decay_scan<NR, false>(q, k, d, v, u, state, cu_q, slot_ids, o, R, H, dk, dv, stream)
+  if (dk <= 32) { JLX_SCAN(8); }
+  if (dk <= 128) { JLX_SCAN(16); }
+  if (dk <= 256) { JLX_SCAN(32); }
+  JLX_SCAN(64);
+#undef JLX_SCAN
+}
+
+// ------------------------------------------------------------------------------------------------ head norm + gate
+// One block per (token, head): out[n, h dv + c] = mult * o[c] / sqrt(mean(o^2) + eps) * weight[(per_head ? h dv : 0) + c]
+// * silu(gate[n, h dv + c]).  weight and gate may be null.  out's rows are ld_out elements apart.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight, int per_head, RowsView gate,
+                                      float eps, float mult, T* __restrict__ out, long long ld_out, int H, int dv) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t n = blockIdx.x;
+  const int hd = blockIdx.y;
+  const float* row = o + (n * H + hd) * dv;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)dv + eps);
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float y = row[c] / rms;
+    if (weight) y *= weight[(per_head ? hd * dv : 0) + c];
+    if (gate.p) {
+      const float g = rows_at(gate, n, hd * dv + c);
+      y *= g / (1.f + expf(-g));
+    }
+    out[n * ld_out + hd * dv + c] = from_f32<T>(mult * y);
+  }
+}
+
+JLX_API int jlx_head_norm_gate(const float* o, const float* weight, int per_head, const RowsView* gate, float eps, float mult,
+                               void* out, int out_dtype, long long ld_out, int N, int H, int dv, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && H > 0 && dv > 0 && H <= 65535 && ld_out >= (long long)H * dv, "head_norm_gate: bad sizes");
+  JLX_REQUIRE(eps > 0.f, "head_norm_gate: eps must be positive");
+  if (N == 0) return 0;
+  RowsView none = {nullptr, 0, 0, 1, 0};
+  const int threads = dv > 128 ? 128 : (dv > 32 ? 64 : 32);
+  JLX_DISPATCH_DTYPE(out_dtype, T, {
+    JLX_CUDA(jlx_launch_pdl(head_norm_gate_kernel<T>, dim3(N, H), dim3(threads), 0, stream, o, weight, per_head,
+                            gate ? *gate : none, eps, mult, (T*)out, ld_out, H, dv));
+  });
+  JLX_LAUNCH_CHECK("head_norm_gate");
+  return 0;
+}

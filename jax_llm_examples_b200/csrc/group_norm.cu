@@ -1,6 +1,7 @@
 // Row kernels of blocks that norm a sublayer's input AND its output ("sandwich" blocks), all with 32-bit math:
 //
-//   group_norm   x += mult * post_w * groupnorm(delta + bias)   (the sublayer's output, normed, scaled, added)
+//   group_norm   x += mult * post_w * groupnorm(delta + bias)   (the sublayer's output, normed, scaled, added;
+//                with post_norm = 0 the norm is left out and post_w is a scale per channel: x += mult * post_w * delta)
 //                out = pre_w * groupnorm(x)                     (the next sublayer's input)
 //                in ONE pass over the row; either half may be missing.  groupnorm cuts a row into equal
 //                consecutive parts and divides each by sqrt(mean(part^2) + eps).
@@ -28,7 +29,7 @@ __device__ __forceinline__ void group_rms(const float* row, int D, int groups, f
 template <typename TO>
 __global__ void group_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, long long split_stride,
                                   const float* __restrict__ delta_bias, const float* __restrict__ post_w, int post_groups,
-                                  float mult, const float* __restrict__ pre_w, int pre_groups, int pre_norm, float eps,
+                                  int post_norm, float mult, const float* __restrict__ pre_w, int pre_groups, int pre_norm, float eps,
                                   TO* __restrict__ out, long long ld_out, float* __restrict__ out32,
                                   const int* __restrict__ row_index, int D) {
   JLX_TL(TL_NORM);
@@ -49,11 +50,11 @@ __global__ void group_norm_kernel(float* __restrict__ x, const float* __restrict
     }
     __syncthreads();
     if (post_w) {
-      group_rms(row, D, post_groups, eps, rms);
+      if (post_norm) group_rms(row, D, post_groups, eps, rms);
       __syncthreads();
       const int gs = D / post_groups;
       for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float y = row[d] / rms[d / gs] * post_w[d];
+        const float y = post_norm ? row[d] / rms[d / gs] * post_w[d] : row[d] * post_w[d];
         const float s = fmaf(mult, y, xr[d]);
         row[d] = s;
         if (!row_index) xr[d] = s;
@@ -101,7 +102,7 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
 template <typename TO>
 __global__ void group_norm_x4_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, long long split_stride,
                                      const float* __restrict__ delta_bias, const float* __restrict__ post_w, int post_groups,
-                                     float mult, const float* __restrict__ pre_w, int pre_groups, int pre_norm, float eps,
+                                     int post_norm, float mult, const float* __restrict__ pre_w, int pre_groups, int pre_norm, float eps,
                                      TO* __restrict__ out, long long ld_out, float* __restrict__ out32,
                                      const int* __restrict__ row_index, int D) {
   JLX_TL(TL_NORM);
@@ -129,17 +130,24 @@ __global__ void group_norm_x4_kernel(float* __restrict__ x, const float* __restr
     }
     __syncthreads();
     if (post_w) {
-      group_rms(row, D, post_groups, eps, rms);
+      if (post_norm) group_rms(row, D, post_groups, eps, rms);
       __syncthreads();
       const int gs4 = (D / post_groups) >> 2;
       for (int d = threadIdx.x; d < D4; d += blockDim.x) {
         const float rr = rms[d / gs4];
         const float4 v = row4[d], w = reinterpret_cast<const float4*>(post_w)[d], xo = xr4[d];
         float4 s;
-        s.x = fmaf(mult, v.x / rr * w.x, xo.x);
-        s.y = fmaf(mult, v.y / rr * w.y, xo.y);
-        s.z = fmaf(mult, v.z / rr * w.z, xo.z);
-        s.w = fmaf(mult, v.w / rr * w.w, xo.w);
+        if (post_norm) {
+          s.x = fmaf(mult, v.x / rr * w.x, xo.x);
+          s.y = fmaf(mult, v.y / rr * w.y, xo.y);
+          s.z = fmaf(mult, v.z / rr * w.z, xo.z);
+          s.w = fmaf(mult, v.w / rr * w.w, xo.w);
+        } else {  // a scale per channel, no norm
+          s.x = fmaf(mult, v.x * w.x, xo.x);
+          s.y = fmaf(mult, v.y * w.y, xo.y);
+          s.z = fmaf(mult, v.z * w.z, xo.z);
+          s.w = fmaf(mult, v.w * w.w, xo.w);
+        }
         row4[d] = s;
         if (!row_index) xr4[d] = s;
       }
@@ -177,11 +185,12 @@ __global__ void group_norm_x4_kernel(float* __restrict__ x, const float* __restr
 }
 
 JLX_API int jlx_group_norm(float* x, const float* delta, int splits, long long split_stride, const float* delta_bias,
-                           const float* post_w, int post_groups, float mult, const float* pre_w, int pre_groups,
-                           int pre_norm, float eps, void* out, int out_dtype, long long ld_out, float* out32,
+                           const float* post_w, int post_groups, int post_norm, float mult, const float* pre_w,
+                           int pre_groups, int pre_norm, float eps, void* out, int out_dtype, long long ld_out, float* out32,
                            const int* row_index, int N, int D, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && splits >= 1, "group_norm: bad sizes N=%d D=%d splits=%d", N, D, splits);
   JLX_REQUIRE(eps > 0.f, "group_norm: eps must be positive");
+  if (!post_norm) post_groups = 1;
   JLX_REQUIRE(!post_w || (post_groups >= 1 && D % post_groups == 0), "group_norm: %d groups do not divide the width %d", post_groups, D);
   JLX_REQUIRE(!pre_norm || (pre_groups >= 1 && D % pre_groups == 0), "group_norm: %d groups do not divide the width %d", pre_groups, D);
   JLX_REQUIRE(!out || ld_out >= D, "group_norm: the output's row is shorter than the width");
@@ -199,7 +208,7 @@ JLX_API int jlx_group_norm(float* x, const float* delta, int splits, long long s
       if (smem > 48 * 1024)
         JLX_CUDA(cudaFuncSetAttribute(group_norm_x4_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       JLX_CUDA(jlx_launch_pdl(group_norm_x4_kernel<TO>, dim3(N), dim3(D >= 8192 ? 512 : (D >= 2048 ? 256 : 128)), smem, stream,
-                              x, delta, splits, split_stride, delta_bias, post_w, post_groups, mult, pre_w, pre_groups, pre_norm,
+                              x, delta, splits, split_stride, delta_bias, post_w, post_groups, post_norm, mult, pre_w, pre_groups, pre_norm,
                               eps, (TO*)out, ld_out, out32, row_index, D));
     });
     JLX_LAUNCH_CHECK("group_norm");
@@ -209,19 +218,21 @@ JLX_API int jlx_group_norm(float* x, const float* delta, int splits, long long s
     if (smem > 48 * 1024)
       JLX_CUDA(cudaFuncSetAttribute(group_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     JLX_CUDA(jlx_launch_pdl(group_norm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, delta, splits, split_stride, delta_bias,
-                            post_w, post_groups, mult, pre_w, pre_groups, pre_norm, eps, (TO*)out, ld_out, out32, row_index, D));
+                            post_w, post_groups, post_norm, mult, pre_w, pre_groups, pre_norm, eps, (TO*)out, ld_out, out32, row_index, D));
   });
   JLX_LAUNCH_CHECK("group_norm");
   return 0;
 }
 
 // ------------------------------------------------------------------------------------------------ bias + activation
-enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3 };
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3, ACT_GELU = 4, ACT_TANH = 5 };
 
 __device__ __forceinline__ float activate(float z, int act) {
   switch (act) {
     case ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
     case ACT_SILU: return z / (1.f + expf(-z));
+    case ACT_GELU: return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    case ACT_TANH: return tanhf(z);
     case ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     default: return z;
   }
@@ -276,7 +287,7 @@ JLX_API int jlx_bias_act(const void* in, int in_dtype, int splits, long long spl
                          int act, void* out, int out_dtype, int rows, int F, cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && F > 0 && splits >= 1, "bias_act: bad sizes rows=%d F=%d splits=%d", rows, F, splits);
   JLX_REQUIRE(splits == 1 || in_dtype == JLX_F32, "bias_act: split-K partials are float32");
-  JLX_REQUIRE(act >= ACT_NONE && act <= ACT_GELU_TANH, "bias_act: unknown activation %d", act);
+  JLX_REQUIRE(act >= ACT_NONE && act <= ACT_TANH, "bias_act: unknown activation %d", act);
   if (rows == 0) return 0;
   if (in_dtype == JLX_F32 && (F & 3) == 0 && (split_stride & 3) == 0 &&
       (((uintptr_t)in | (uintptr_t)bias | (uintptr_t)add) & 15) == 0) {

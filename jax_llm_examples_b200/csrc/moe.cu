@@ -13,8 +13,18 @@
 
 // One block per token.  Warp w computes the scores of experts w, w + nwarp, ...: a fixed order of
 // the D products per (token, expert), so a token's routing does not depend on the batch.
+// bias (null: none) is added to the scores before the choice.  weight_form 0: sigmoid of the chosen score;
+// 1: softmax over the chosen scores only.
+__device__ __forceinline__ void softmax_of_chosen(float* w, int k) {
+  float m = -INFINITY, sum = 0.f;
+  for (int j = 0; j < k; ++j) m = fmaxf(m, w[j]);
+  for (int j = 0; j < k; ++j) sum += expf(w[j] - m);
+  for (int j = 0; j < k; ++j) w[j] = expf(w[j] - m) / sum;
+}
+
 __global__ void router_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
-                              float* __restrict__ topk_w, float* __restrict__ scores_out, int D, int E, int k) {
+                              float* __restrict__ topk_w, float* __restrict__ scores_out, int D, int E, int k,
+                              const float* __restrict__ bias, int weight_form) {
   JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_MAX_E];
   const int n = blockIdx.x;
@@ -25,7 +35,7 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
     float s = 0.f;
     for (int d = lane; d < D; d += 32) s = fmaf(hr[d], wr[d], s);
     s = warp_sum(s);
-    if (lane == 0) scores[e] = s;
+    if (lane == 0) scores[e] = bias ? s + bias[e] : s;
   }
   __syncthreads();
   if (scores_out)
@@ -44,9 +54,10 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
       }
       if (best < 0) best = j;  // all NaN: still a valid expert index
       topk_idx[(size_t)n * k + j] = best;
-      topk_w[(size_t)n * k + j] = 1.f / (1.f + expf(-bv));
+      topk_w[(size_t)n * k + j] = weight_form == 1 ? bv : 1.f / (1.f + expf(-bv));
       scores[best] = NAN;  // taken
     }
+    if (weight_form == 1) softmax_of_chosen(topk_w + (size_t)n * k, k);
   }
 }
 
@@ -59,7 +70,7 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
 template <int EPW>
 __global__ void __launch_bounds__(256, 2)
 router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
-                   float* __restrict__ topk_w, int N, int D, int E, int k) {
+                   float* __restrict__ topk_w, int N, int D, int E, int k, const float* __restrict__ bias, int weight_form) {
   JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_ROWS][ROUTER_MAX_E];
   pdl_launch_dependents();
@@ -94,7 +105,7 @@ router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_rout
 #pragma unroll
       for (int r = 0; r < ROUTER_ROWS; ++r) {
         const float s = warp_sum(acc[i][r]);
-        if (lane == 0 && e0 + i < E) scores[r][e0 + i] = s;
+        if (lane == 0 && e0 + i < E) scores[r][e0 + i] = bias ? s + bias[e0 + i] : s;
       }
   }
   __syncthreads();
@@ -114,28 +125,30 @@ router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_rout
       }
       if (best < 0) best = j;  // all NaN: still a valid expert index
       topk_idx[n * k + j] = best;
-      topk_w[n * k + j] = 1.f / (1.f + expf(-bv));
+      topk_w[n * k + j] = weight_form == 1 ? bv : 1.f / (1.f + expf(-bv));
       sc[best] = NAN;  // taken
     }
+    if (weight_form == 1) softmax_of_chosen(topk_w + n * k, k);
   }
 }
 
 // many_rows: the kernel that shares router rows among eight tokens (another order of the sums than the
 // one-token kernel's: a caller whose results must not depend on the batch uses one of the two throughout).
 JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, float* topk_w, float* scores_out, int N,
-                       int D, int E, int k, int many_rows, cudaStream_t stream) {
+                       int D, int E, int k, int many_rows, const float* bias, int weight_form, cudaStream_t stream) {
+  JLX_REQUIRE(weight_form == 0 || weight_form == 1, "router: unknown weight form %d", weight_form);
   JLX_REQUIRE(N >= 0 && D > 0, "router: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(E >= 1 && E <= ROUTER_MAX_E, "router: %d experts; supported 1..%d", E, ROUTER_MAX_E);
   JLX_REQUIRE(k >= 1 && k <= E && k <= ROUTER_MAX_K, "router: top-%d of %d experts; supported k in 1..min(E, %d)", k, E, ROUTER_MAX_K);
   if (N == 0) return 0;
   if (many_rows && !scores_out && D % 4 == 0 && (((uintptr_t)h | (uintptr_t)w_router) & 15) == 0) {
     const dim3 grid((N + ROUTER_ROWS - 1) / ROUTER_ROWS);
-    if (E <= 16) JLX_CUDA(jlx_launch_pdl(router_rows_kernel<2>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k));
-    else JLX_CUDA(jlx_launch_pdl(router_rows_kernel<4>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k));
+    if (E <= 16) JLX_CUDA(jlx_launch_pdl(router_rows_kernel<2>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form));
+    else JLX_CUDA(jlx_launch_pdl(router_rows_kernel<4>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k, bias, weight_form));
     JLX_LAUNCH_CHECK("router_rows");
     return 0;
   }
-  router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k);
+  router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k, bias, weight_form);
   JLX_LAUNCH_CHECK("router");
   return 0;
 }
@@ -223,7 +236,7 @@ __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __r
   pdl_wait();
   const int i = blockIdx.x;
   const int pair = i < P ? sorted_pair[i] : 0;
-  const float w = i < P ? topk_w[pair] : 1.f;
+  const float w = i < P && topk_w ? topk_w[pair] : 1.f;  // no weights: the rows are gathered unscaled
   const float* src = h + (size_t)(i < P ? pair / k : i - P) * D;
   T* dst = a_sorted + (size_t)i * D;
   if ((D & 3) == 0) {  // rows are 16-byte aligned: four elements per thread and access
@@ -250,12 +263,13 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
   return 0;
 }
 
-// delta[n, :] = sum_j y[sorted_pos[n * k + j], :]  (+ y[extra_base + n, :] if extra_base >= 0: the appended
+// delta[n, :] = sum_j (pair_w ? pair_w[n * k + j] : 1) * y[sorted_pos[n * k + j], :]  (+ y[extra_base + n, :] if extra_base >= 0: the appended
 // shared-expert group)  (+ shared[n, :]), where y and shared may be split-K partials [z][rows][D] that are
 // added first, z ascending; j ascending: a fixed order.
 __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, long long y_stride, int extra_base,
                                    const float* __restrict__ shared, int splits, long long split_stride,
-                                   const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
+                                   const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k,
+                                   const float* __restrict__ pair_w) {
   JLX_TL(TL_MOE_COMBINE);
   pdl_launch_dependents();
   pdl_wait();
@@ -273,6 +287,16 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
         for (int z = 0; z < y_splits; ++z) add(y + (size_t)z * y_stride + (size_t)(extra_base + n) * D + d);
       for (int j = 0; j < k; ++j) {
         const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
+        if (pair_w) {  // the expert's OUTPUT is weighted: its partials are added first, then scaled
+          float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int z = 0; z < y_splits; ++z) {
+            const float4 v = *reinterpret_cast<const float4*>(y + (size_t)z * y_stride + row);
+            e.x += v.x; e.y += v.y; e.z += v.z; e.w += v.w;
+          }
+          const float w = pair_w[(size_t)n * k + j];
+          s.x = fmaf(w, e.x, s.x); s.y = fmaf(w, e.y, s.y); s.z = fmaf(w, e.z, s.z); s.w = fmaf(w, e.w, s.w);
+          continue;
+        }
         for (int z = 0; z < y_splits; ++z) add(y + (size_t)z * y_stride + row);
       }
       *reinterpret_cast<float4*>(delta + (size_t)n * D + d) = s;
@@ -287,6 +311,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
       for (int z = 0; z < y_splits; ++z) s += y[(size_t)z * y_stride + (size_t)(extra_base + n) * D + d];
     for (int j = 0; j < k; ++j) {
       const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
+      if (pair_w) {
+        float e = 0.f;
+        for (int z = 0; z < y_splits; ++z) e += y[(size_t)z * y_stride + row];
+        s = fmaf(pair_w[(size_t)n * k + j], e, s);
+        continue;
+      }
       for (int z = 0; z < y_splits; ++z) s += y[(size_t)z * y_stride + row];
     }
     delta[(size_t)n * D + d] = s;
@@ -295,11 +325,11 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
 
 JLX_API int jlx_moe_combine(const float* y, int y_splits, long long y_stride, int extra_base, const float* shared,
                             int splits, long long split_stride, const int* sorted_pos, float* delta, int N, int D, int k,
-                            cudaStream_t stream) {
+                            const float* pair_w, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1 && y_splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
   const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;  // four columns per thread: 1024 columns per block
   JLX_CUDA(jlx_launch_pdl(moe_combine_kernel, dim3(N, ysplit), dim3(256), 0, stream, y, y_splits, y_stride, extra_base, shared,
-                          splits, split_stride, sorted_pos, delta, D, k));
+                          splits, split_stride, sorted_pos, delta, D, k, pair_w));
   return 0;
 }

@@ -377,3 +377,151 @@ JLX_API int jlx_kv_store(const void* k, const void* v, void* pages, int dtype, c
   JLX_LAUNCH_CHECK("kv_store");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same pass for attention whose q and k are normed with a weight BEFORE the rotation, rotated in the "rotate half"
+// layout on their first rot_dims entries only, and whose values may have another size than its keys.
+//
+//   q, k:  y = x / sqrt(mean(x^2) + eps) * w   over the head's dk entries (w: [dk], shared by the heads; null = no norm)
+//          (y_i, y_(i + rot/2)) <- (y_i cos a - y_(i + rot/2) sin a,  y_(i + rot/2) cos a + y_i sin a),
+//          a = position * inv_freq[i], i < rot / 2; entries from rot on pass unchanged.
+//
+// The projected rows are float32 (split-K partials are added first) with the q heads from column 0, the k heads from
+// column k_col and the v heads (dv entries each) from column v_col.  q_out and the cache keep `dpad` entries per head:
+// keys, queries and values are padded with zeros up to it, so that one page layout and the attention kernels built
+// for equal sizes serve keys of one size and values of another.
+struct RopeRowsView {
+  const float* p;
+  long long split_stride;
+  long long ld;
+  int splits;
+  int pad_;
+};
+
+template <typename T>
+__global__ void rope_half_kv_store_kernel(RopeRowsView proj, int k_col, int v_col, T* __restrict__ q_out, T* __restrict__ pages,
+                                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ req_of_token,
+                                          const int* __restrict__ positions, const float* __restrict__ q_norm_w,
+                                          const float* __restrict__ k_norm_w, float eps, const float* __restrict__ inv_freq,
+                                          int rot, int Hq, int Hkv, int dk, int dv, int dpad, int page_size, int num_pages,
+                                          int store, int* status) {
+  JLX_TL(TL_ROPE);
+  pdl_launch_dependents_if_small();
+  extern __shared__ float buf[];  // [warps][max(dk, dv)]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const size_t n = blockIdx.x;
+  const int dmax = dk > dv ? dk : dv;
+  float* row = buf + warp * dmax;
+  pdl_wait();
+  const int pos = positions[n];
+  const int half = rot >> 1;
+  T* kdst = nullptr;
+  if (store) {
+    const int page = block_table[(size_t)req_of_token[n] * bt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, JLX_STATUS_BAD_PAGE);
+    } else {
+      kdst = pages + ((size_t)page * 2 * Hkv * page_size + (size_t)(pos % page_size)) * dpad;
+    }
+  }
+  const int heads = Hq + (store ? 2 * Hkv : 0);
+  for (int hh = blockIdx.y * nwarp + warp; hh < heads; hh += gridDim.y * nwarp) {
+    const bool is_q = hh < Hq, is_k = !is_q && hh < Hq + Hkv;
+    const int d = is_q || is_k ? dk : dv;
+    const int col = is_q ? hh * dk : (is_k ? k_col + (hh - Hq) * dk : v_col + (hh - Hq - Hkv) * dv);
+    T* dst;
+    if (is_q) dst = q_out + (n * Hq + hh) * dpad;
+    else if (!kdst) continue;
+    else dst = kdst + (size_t)((is_k ? hh - Hq : Hkv + hh - Hq - Hkv)) * page_size * dpad;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      float s = 0.f;
+      for (int z = 0; z < proj.splits; ++z) s += proj.p[(size_t)z * proj.split_stride + n * proj.ld + col + i];
+      row[i] = s;
+      ss = fmaf(s, s, ss);
+    }
+    const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if ((is_q || is_k) && w) {
+      ss = warp_sum(ss);
+      const float rms = sqrtf(ss / (float)d + eps);
+      __syncwarp();
+      for (int i = lane; i < d; i += 32) row[i] = row[i] / rms * w[i];
+    }
+    __syncwarp();
+    for (int i = lane; i < dpad; i += 32) {
+      float y = 0.f;
+      if (i < d) {
+        y = row[i];
+        if ((is_q || is_k) && i < rot) {
+          const int f = i < half ? i : i - half;
+          float sn, cs;
+          sincosf((float)pos * inv_freq[f], &sn, &cs);
+          y = i < half ? row[i] * cs - row[i + half] * sn : row[i] * cs + row[i - half] * sn;
+        }
+      }
+      dst[i] = from_f32<T>(y);
+    }
+    __syncwarp();
+  }
+}
+
+// proj: float32 rows (see RopeRowsView; p points at the first q column).  pages: [P, 2, Hkv, page_size, dpad] or null.
+JLX_API int jlx_rope_half_kv_store(const RopeRowsView* proj, int k_col, int v_col, void* q_out, void* pages, int dtype,
+                                   const int* block_table, int bt_stride, const int* req_of_token, const int* positions,
+                                   const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rot,
+                                   int N, int Hq, int Hkv, int dk, int dv, int dpad, int page_size, int num_pages, int store,
+                                   int* status, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && dk > 0 && dv > 0, "rope_half: bad sizes");
+  JLX_REQUIRE(dpad >= dk && dpad >= dv, "rope_half: the padded head size %d is below the key or value size (%d, %d)", dpad, dk, dv);
+  JLX_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk, "rope_half: %d rotated entries of %d", rot, dk);
+  JLX_REQUIRE(rot == 0 || inv_freq, "rope_half: frequencies missing");
+  JLX_REQUIRE(!store || (pages && block_table && page_size > 0 && num_pages > 0), "rope_half: cache missing");
+  if (N == 0) return 0;
+  const int heads = Hq + (store ? 2 * Hkv : 0);
+  const int nwarp = heads < 8 ? heads : 8;
+  const int by = N >= 64 ? 1 : (heads + nwarp - 1) / nwarp;
+  const size_t smem = sizeof(float) * (size_t)nwarp * (dk > dv ? dk : dv);
+  JLX_REQUIRE(smem <= 48 * 1024, "rope_half: head size too large");
+  JLX_DISPATCH_DTYPE(dtype, T, {
+    JLX_CUDA(jlx_launch_pdl(rope_half_kv_store_kernel<T>, dim3(N, by), dim3(nwarp * 32), smem, stream, *proj, k_col, v_col,
+                            (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token, positions, q_norm_w, k_norm_w, eps,
+                            inv_freq, rot, Hq, Hkv, dk, dv, dpad, page_size, num_pages, store, status));
+  });
+  JLX_LAUNCH_CHECK("rope_half_kv_store");
+  return 0;
+}
+
+// out[n, h dv + c] = mult * sigmoid(gate[n, h]) * attn[n, h, c], c < dv: the attention's heads (dpad entries each, of
+// which dv count) through a gate per token and head, into (a column range of) the rows that the output product reads.
+// gate: float32 rows, possibly split-K partials (p null: no gate).
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ attn, RopeRowsView gate, float mult, T* __restrict__ out, long long ld_out,
+                                 int Hq, int dv, int dpad) {
+  JLX_TL(TL_OTHER);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t n = blockIdx.x;
+  for (int idx = threadIdx.x; idx < Hq * dv; idx += blockDim.x) {
+    const int hd = idx / dv, c = idx - hd * dv;
+    float g = mult;
+    if (gate.p) {
+      float s = 0.f;
+      for (int z = 0; z < gate.splits; ++z) s += gate.p[(size_t)z * gate.split_stride + n * gate.ld + hd];
+      g *= 1.f / (1.f + expf(-s));
+    }
+    out[n * ld_out + idx] = from_f32<T>(g * to_f32<T>(attn[(n * Hq + hd) * dpad + c]));
+  }
+}
+
+JLX_API int jlx_head_gate(const void* attn, const RopeRowsView* gate, float mult, void* out, int dtype, long long ld_out, int N,
+                          int Hq, int dv, int dpad, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && Hq > 0 && dv > 0 && dpad >= dv && ld_out >= (long long)Hq * dv, "head_gate: bad sizes");
+  if (N == 0) return 0;
+  RopeRowsView none = {nullptr, 0, 0, 1, 0};
+  JLX_DISPATCH_DTYPE(dtype, T, {
+    JLX_CUDA(jlx_launch_pdl(head_gate_kernel<T>, dim3(N), dim3(Hq * dv >= 1024 ? 256 : 128), 0, stream, (const T*)attn,
+                            gate ? *gate : none, mult, (T*)out, ld_out, Hq, dv, dpad));
+  });
+  JLX_LAUNCH_CHECK("head_gate");
+  return 0;
+}

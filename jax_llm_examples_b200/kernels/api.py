@@ -204,16 +204,18 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: 
 
 
 # ------------------------------------------------------- grouped norms around a sublayer, biases, short convolution
-ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}  # csrc/group_norm.cu
+ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3, "gelu": 4, "tanh": 5}  # csrc/group_norm.cu ("gelu": the exact, erf form)
 
 
 def group_norm(x: torch.Tensor, delta: torch.Tensor | None = None, delta_splits: int = 1, delta_bias: torch.Tensor | None = None,
                post_weight: torch.Tensor | None = None, post_groups: int = 1, mult: float = 1.0,
                pre_weight: torch.Tensor | None = None, pre_groups: int = 1, pre_norm: bool = True, eps: float = 1e-6,
-               out: torch.Tensor | None = None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None) -> None:
+               out: torch.Tensor | None = None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None,
+               post_norm: bool = True) -> None:
     """One pass over each row of the float32 residual x [N, D]:
     x += mult * post_weight * groupnorm(delta + delta_bias) (``delta``: float32 [N, D] or ``delta_splits`` partials of
-    it; without post_weight the sum is added as it is), then out / out32 = pre_weight * groupnorm(x) (``pre_norm``
+    it; without post_weight the sum is added as it is; with ``post_norm`` False post_weight is a plain scale per
+    channel: x += mult * post_weight * delta), then out / out32 = pre_weight * groupnorm(x) (``pre_norm``
     False: x itself).  groupnorm divides each of ``groups`` equal consecutive parts of a row by
     sqrt(mean(part^2) + eps).  ``out`` may be a view whose rows are longer than D (its row stride is kept).  With
     row_index, row n reads source row row_index[n] and x is not written back."""
@@ -228,7 +230,7 @@ def group_norm(x: torch.Tensor, delta: torch.Tensor | None = None, delta_splits:
         ld_out = out.stride(0) if N > 1 else D
     sp, stride = _splits(delta, delta_splits)
     _run("group_norm", "jlx_group_norm", _ptr(x), _ptr(delta), c_int(sp), c_longlong(stride), _ptr(delta_bias),
-         _ptr(post_weight), c_int(post_groups), c_float(mult), _ptr(pre_weight), c_int(pre_groups), c_int(int(pre_norm)),
+         _ptr(post_weight), c_int(post_groups), c_int(int(post_norm)), c_float(mult), _ptr(pre_weight), c_int(pre_groups), c_int(int(pre_norm)),
          c_float(eps), _ptr(out), c_int(code(out.dtype) if out is not None else F32), c_longlong(ld_out), _ptr(out32),
          _ptr(row_index), c_int(N), c_int(D), _stream())
 
@@ -430,6 +432,117 @@ def heads_to_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     _run("attention_latent", "jlx_heads_to_rows", _ptr(x), _ptr(out), c_int(code(x.dtype)), c_int(N), c_int(H), c_int(d), _stream())
 
 
+# ------------------------------------------------------ linear attention with a decay per key channel
+class _RowsView(ctypes.Structure):  # RowsView in csrc/decay_scan.cu, RopeRowsView in csrc/rope_kv.cu
+    _fields_ = [("p", c_void_p), ("split_stride", c_longlong), ("ld", c_longlong), ("splits", c_int), ("pad_", c_int)]
+
+
+def rows_view(data: torch.Tensor, splits: int = 1, col: int = 0, row: int = 0) -> _RowsView:
+    """Columns from ``col`` on (rows from ``row`` on) of float32 projected rows [N, F] or split-K partials [splits, N, F]."""
+    if data.dtype != torch.float32 or not data.is_contiguous() or not data.is_cuda:
+        raise KernelError("projected rows must be contiguous float32 on the GPU")
+    F = data.shape[-1]
+    sp, stride = _splits(data, splits)
+    v = _RowsView()
+    v.p, v.split_stride, v.ld, v.splits = data.data_ptr() + 4 * (row * F + col), stride, F, sp
+    return v
+
+
+def token_shift_blend(h32: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor,
+                      req_of_token: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, n] = h[n] + (h_prev[n] - h[n]) * mu[m], h_prev the request's previous token: the row before, or for a
+    step's first token of a request its state (float32 [slots, D], zeros at the start), which then becomes the
+    step's last row of the request.  h32: float32 [N, D]; mu: float32 [M, D]; out: [M, N, D]."""
+    _contig(h32, mu, state, out)
+    N, D = h32.shape
+    M = mu.shape[0]
+    if any(t.dtype != torch.float32 for t in (h32, mu, state)) or tuple(out.shape) != (M, N, D) or tuple(state.shape[1:]) != (D,):
+        raise KernelError("token_shift_blend: float32 rows, blend weights and state [slots, D] and out [M, N, D] are needed")
+    _run("decay_scan", "jlx_token_shift_blend", _ptr(h32), _ptr(mu), _ptr(state), _ptr(cu_q), _ptr(slot_ids), _ptr(req_of_token),
+         _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(slot_ids.numel()), c_int(D), c_int(M), _stream())
+
+
+DECAY_FORMS = {"double_exp": 0, "sigmoid_power": 1}  # csrc/decay_scan.cu
+
+
+def decay_prep(q: _RowsView, k: _RowsView, v: _RowsView, z: _RowsView, z_bias: torch.Tensor | None, form: str, tau: float,
+               q_scale: float, qo: torch.Tensor, ko: torch.Tensor, do: torch.Tensor, vo: torch.Tensor, heads: int, dk: int,
+               dv: int) -> None:
+    """qo = q_scale * q, ko = k, vo = v, do = the decay of every key channel: exp(-exp(z + bias)) ("double_exp") or
+    sigmoid(z + bias)^(1 / tau) ("sigmoid_power"), all float32 [N, H, dk] ([N, H, dv] for vo), from projected rows."""
+    _contig(z_bias, qo, ko, do, vo)
+    N = qo.shape[0]
+    if any(t.dtype != torch.float32 for t in (qo, ko, do, vo)) or (z_bias is not None and z_bias.dtype != torch.float32):
+        raise KernelError("decay_prep: float32 outputs and bias are needed")
+    _run("decay_scan", "jlx_decay_prep", ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(z), _ptr(z_bias),
+         c_int(DECAY_FORMS[form]), c_float(tau), c_float(q_scale), _ptr(qo), _ptr(ko), _ptr(do), _ptr(vo), c_int(N), c_int(heads),
+         c_int(dk), c_int(dv), _stream())
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, d: torch.Tensor, v: torch.Tensor, bonus: torch.Tensor | None, state: torch.Tensor,
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, o: torch.Tensor, read_after_update: bool) -> None:
+    """S <- diag(d_t) S + k_t v_t^T over each request's tokens, in order.  ``read_after_update``: o_t = S_t^T q_t; else
+    o_t = (S_(t-1) + diag(bonus) k_t v_t^T)^T q_t.  q, k, d: float32 [N, H, dk]; v, o: [N, H, dv]; bonus: [H, dk];
+    state: float32 [slots, H, dk, dv]."""
+    _contig(q, k, d, v, bonus, state, o)
+    N, H, dk = q.shape
+    dv = v.shape[2]
+    if any(t.dtype != torch.float32 for t in (q, k, d, v, state, o)) or (bonus is not None and bonus.dtype != torch.float32):
+        raise KernelError("decay_scan: everything is float32")
+    if tuple(state.shape[1:]) != (H, dk, dv) or tuple(o.shape) != (N, H, dv) or (bonus is not None and bonus.numel() != H * dk):
+        raise KernelError(f"decay_scan: shapes do not fit: q {tuple(q.shape)}, v {tuple(v.shape)}, state {tuple(state.shape)}")
+    _run("decay_scan", "jlx_decay_scan", _ptr(q), _ptr(k), _ptr(d), _ptr(v), _ptr(bonus), _ptr(state), _ptr(cu_q), _ptr(slot_ids),
+         _ptr(o), c_int(slot_ids.numel()), c_int(H), c_int(dk), c_int(dv), c_int(int(read_after_update)), _stream())
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor | None, per_head: bool, gate: _RowsView | None, eps: float, mult: float,
+                   out: torch.Tensor) -> None:
+    """out[n, h dv + c] = mult * o[n, h, c] / sqrt(mean_c(o[n, h]^2) + eps) * weight * silu(gate[n, h dv + c]).
+    o: float32 [N, H, dv]; weight: float32 [H dv] (``per_head``) or [dv] (shared by the heads) or None; out: [N, H dv],
+    possibly a column range of wider rows."""
+    _contig(o, weight)
+    N, H, dv = o.shape
+    if o.dtype != torch.float32 or (weight is not None and (weight.dtype != torch.float32 or weight.numel() != (H * dv if per_head else dv))):
+        raise KernelError("head_norm_gate: float32 rows and a weight of H * dv (per head) or dv entries are needed")
+    if out.shape != (N, H * dv) or out.stride(1) != 1:
+        raise KernelError("head_norm_gate: out must be [N, H * dv] with contiguous rows")
+    _run("decay_scan", "jlx_head_norm_gate", _ptr(o), _ptr(weight), c_int(int(per_head)), ctypes.byref(gate) if gate is not None else None,
+         c_float(eps), c_float(mult), _ptr(out), c_int(code(out.dtype)), c_longlong(out.stride(0) if N > 1 else H * dv), c_int(N),
+         c_int(H), c_int(dv), _stream())
+
+
+# ---------------------------------- weighted q/k norm + rotate-half rotation + page write; gated attention heads
+def rope_half_kv_store(proj: _RowsView, k_col: int, v_col: int, q_out: torch.Tensor, pages: torch.Tensor | None,
+                       block_table: torch.Tensor | None, req_of_token: torch.Tensor, positions: torch.Tensor,
+                       q_norm_weight: torch.Tensor | None, k_norm_weight: torch.Tensor | None, eps: float,
+                       inv_freq: torch.Tensor | None, rot_dims: int, Hq: int, Hkv: int, dk: int, dv: int, status: torch.Tensor) -> None:
+    """From projected float32 rows (q heads from the view's first column, k heads from column k_col, v heads of dv
+    entries from v_col): q and k RMS-normed over dk with a weight, then their first rot_dims entries rotated (entry i
+    paired with i + rot_dims / 2); q into q_out [N, Hq, dpad], k and v into the token's cache row
+    (pages [P, 2, Hkv, page_size, dpad]), all padded with zeros to dpad."""
+    _contig(q_out, pages, block_table, q_norm_weight, k_norm_weight, inv_freq)
+    N, _, dpad = q_out.shape
+    store = pages is not None
+    if store and (pages.dtype != q_out.dtype or tuple(pages.shape[1:3]) != (2, Hkv) or pages.shape[4] != dpad):
+        raise KernelError(f"rope_half_kv_store: pages {tuple(pages.shape)} do not fit {Hkv} heads padded to {dpad}")
+    _run("rope_kv", "jlx_rope_half_kv_store", ctypes.byref(proj), c_int(k_col), c_int(v_col), _ptr(q_out), _ptr(pages),
+         c_int(code(q_out.dtype)), _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token),
+         _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps), _ptr(inv_freq), c_int(rot_dims), c_int(N),
+         c_int(Hq), c_int(Hkv), c_int(dk), c_int(dv), c_int(dpad), c_int(pages.shape[3] if store else 0),
+         c_int(pages.shape[0] if store else 0), c_int(int(store)), _ptr(status), _stream())
+
+
+def head_gate(attn: torch.Tensor, gate: _RowsView | None, mult: float, out: torch.Tensor, dv: int) -> None:
+    """out[n, h dv + c] = mult * sigmoid(gate[n, h]) * attn[n, h, c] for c < dv.  attn: [N, Hq, dpad]; gate: float32
+    projected rows (None: no gate); out: [N, Hq dv], possibly a column range of wider rows."""
+    _contig(attn)
+    N, Hq, dpad = attn.shape
+    if out.shape != (N, Hq * dv) or out.stride(1) != 1 or out.dtype != attn.dtype:
+        raise KernelError("head_gate: out must be [N, Hq * dv] of the attention's type with contiguous rows")
+    _run("rope_kv", "jlx_head_gate", _ptr(attn), ctypes.byref(gate) if gate is not None else None, c_float(mult), _ptr(out),
+         c_int(code(attn.dtype)), c_longlong(out.stride(0) if N > 1 else Hq * dv), c_int(N), c_int(Hq), c_int(dv), c_int(dpad), _stream())
+
+
 # ------------------------------------------------------------------- position encoding + cache
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor | None, block_table: torch.Tensor | None,
                   req_of_token: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, l2norm: bool,
@@ -606,18 +719,23 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: tor
 
 
 # --------------------------------------------------------------------------------------- MoE
+ROUTER_WEIGHT_FORMS = {"sigmoid": 0, "softmax_of_chosen": 1}  # csrc/moe.cu
+
+
 def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
-           scores_out: torch.Tensor | None = None, many_rows: bool = False) -> None:
-    """Scores h32 @ w_router^T in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
+           scores_out: torch.Tensor | None = None, many_rows: bool = False, bias: torch.Tensor | None = None,
+           weight_form: str = "sigmoid") -> None:
+    """Scores h32 @ w_router^T (+ bias) in 32-bit, top-k of the scores (lower index wins ties); the weights are the
+    sigmoid of each chosen score, or (``weight_form`` "softmax_of_chosen") the softmax over the chosen scores only.
     ``many_rows``: the kernel that shares each router row among eight tokens (for prompt portions; its sums
     run in another order than the one-token kernel's)."""
-    _contig(h32, w_router, topk_idx, topk_w, scores_out)
+    _contig(h32, w_router, topk_idx, topk_w, scores_out, bias)
     N, D = h32.shape
     E, k = w_router.shape[0], topk_idx.shape[1]
-    if h32.dtype != torch.float32 or w_router.dtype != torch.float32:
-        raise KernelError("router: scores are computed from float32 input and weight")
+    if h32.dtype != torch.float32 or w_router.dtype != torch.float32 or (bias is not None and bias.dtype != torch.float32):
+        raise KernelError("router: scores are computed from float32 input, weight and bias")
     _run("moe", "jlx_router", _ptr(h32), _ptr(w_router), _ptr(topk_idx), _ptr(topk_w), _ptr(scores_out), c_int(N),
-         c_int(D), c_int(E), c_int(k), c_int(int(many_rows)), _stream())
+         c_int(D), c_int(E), c_int(k), c_int(int(many_rows)), _ptr(bias), c_int(ROUTER_WEIGHT_FORMS[weight_form]), _stream())
 
 
 def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,
@@ -638,9 +756,10 @@ def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torc
          _ptr(status), _stream())
 
 
-def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor, a_sorted: torch.Tensor, k: int,
+def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor | None, a_sorted: torch.Tensor, k: int,
                   extra_rows: int = 0) -> None:
-    """a_sorted[i] = weight * h32[token] in expert order; then extra_rows unscaled copies of h32's rows."""
+    """a_sorted[i] = weight * h32[token] in expert order (``topk_w`` None: unscaled); then extra_rows unscaled copies
+    of h32's rows."""
     _contig(h32, sorted_pair, topk_w, a_sorted)
     P = a_sorted.shape[0] - extra_rows
     _run("moe", "jlx_permute_scale", _ptr(h32), _ptr(sorted_pair), _ptr(topk_w), _ptr(a_sorted),
@@ -648,15 +767,16 @@ def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Te
 
 
 def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int,
-                shared_splits: int = 1, y_splits: int = 1, extra_base: int = -1) -> None:
+                shared_splits: int = 1, y_splits: int = 1, extra_base: int = -1, pair_weights: torch.Tensor | None = None) -> None:
     """delta = the sum of each token's expert rows (+ row extra_base + n of y: an appended shared group)
-    (+ shared); y_sorted and shared may be split-K partials."""
-    _contig(y_sorted, shared, sorted_pos, delta)
+    (+ shared); y_sorted and shared may be split-K partials.  ``pair_weights`` (float32 [N, k]): each expert row is
+    multiplied by its (token, choice) weight as it is added (experts whose OUTPUT is weighted)."""
+    _contig(y_sorted, shared, sorted_pos, delta, pair_weights)
     N, D = delta.shape
     sp, stride = _splits(shared, shared_splits)
     ysp, ystride = _splits(y_sorted, y_splits)
     _run("moe", "jlx_moe_combine", _ptr(y_sorted), c_int(ysp), c_longlong(ystride), c_int(extra_base), _ptr(shared),
-         c_int(sp), c_longlong(stride), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D), c_int(k), _stream())
+         c_int(sp), c_longlong(stride), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D), c_int(k), _ptr(pair_weights), _stream())
 
 
 # ---------------------------------------------------------------------------------- sampling

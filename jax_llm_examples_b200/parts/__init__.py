@@ -1,17 +1,21 @@
-from .attention import PagedAttention, plan_attention_tiles
-from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, PostNormed, Rows, RowSum, Runtime, StateNeed,
+from .attention import GatedPagedAttention, PagedAttention, plan_attention_tiles
+from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, PostNormed, ProjectedMixer, Rows, RowSum, Runtime, Scaled, StateNeed,
                    StepContext, StepShape, Workspace, as_rows, known_parts, make_part, register_part)
-from .block import PreNormBlock, ReinjectionBlock, SandwichNormBlock
+from .block import PreNormBlock, ReinjectionBlock, SandwichNormBlock, ScaledPreNormBlock
 from .conv import ResidualShortConv
 from .decoder import CachePlan, DecoderModel, LayerRun
-from .feedforward import DenseBiasedMLP, DenseSwiGLU, RoutedExperts
+from .feedforward import DenseBiasedMLP, DenseSwiGLU, RoutedExperts, SoftmaxRoutedMLPExperts
 from .latent_attention import LatentAttention, rotary_frequencies
+from .linear_attention import GatedLinearAttention, TimeMixWKV
 from .linear import grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
+from .parallel import ParallelMixers
 from .norms import GroupRMSNorm, RMSNorm, add_to_residual
 from .recurrent import HGRN2, InputConvMixer
 from .positions import InterleavedRope, NoPositionWithTemperature, UnfusedEncoding, llama3_scaled_frequencies
 
 __all__ = [
+    "GatedLinearAttention", "GatedPagedAttention", "ParallelMixers", "ProjectedMixer", "Scaled", "ScaledPreNormBlock",
+    "SoftmaxRoutedMLPExperts", "TimeMixWKV",
     "DenseBiasedMLP", "GroupRMSNorm", "HGRN2", "InputConvMixer", "LatentAttention", "PostNormed", "ReinjectionBlock",
     "ResidualShortConv", "SandwichNormBlock", "add_to_residual", "rotary_frequencies",
     "Block", "CachePlan", "DecoderModel", "DenseSwiGLU", "FeedForward", "InterleavedRope", "KVNeed", "LayerCache",

@@ -8,7 +8,7 @@ import torch
 from ..cache.manager import Retention
 from ..kernels import api as K
 from ..tracing import scope
-from .base import KVNeed, LayerCache, Mixer, PositionEncoding, Runtime, StepContext, StepShape, register_part
+from .base import KVNeed, LayerCache, Mixer, PositionEncoding, ProjectedMixer, Rows, Runtime, StepContext, StepShape, register_part
 from .linear import linear
 
 # How this part's kernels cut a step's tokens (the planner below is theirs alone; nothing else knows these numbers).
@@ -158,3 +158,83 @@ class PagedAttention(Mixer):
 
 
 register_part("mixer", "paged_attention", PagedAttention)
+
+
+class GatedPagedAttention(ProjectedMixer, PagedAttention):
+    """Grouped-query softmax attention over the paged cache whose queries and keys are RMS-normed with a weight BEFORE
+    they are rotated, rotated on their first ``rot_dims`` entries only in the rotate-half layout (entry i pairs with
+    i + rot_dims / 2, angle position * rot_base^(-2i / rot_dims)), whose values may have another size than its keys, and
+    whose heads pass a sigmoid gate, one number per token and head, before the output product:
+
+        out = W_o [ sigmoid(W_g h)_a * softmax(scale * q_a K^T) V  for every head a ]
+
+    ``w_in``: [Hq dk + Hkv dk + Hkv dv (+ Hq), D] = the q, k, v and gate projections stacked in that order (no gate rows:
+    no gate).  ``q_norm_weight`` / ``k_norm_weight``: [dk], shared by the heads; None = no norm.  ``window``: a query
+    sees itself and the window - 1 positions before it.  Keys, queries and values are kept at one padded size
+    (``padded_dim`` >= max(dk, dv), zeros beyond their own): one page layout, and the attention kernels built for
+    equal sizes, serve both.  It is a :class:`ProjectedMixer`: beside another mixer that reads the same input, both
+    share their input and output products."""
+
+    kernel_libraries = ("attention_generic", "gemm_simt", "rope_kv")
+    kernel_libraries_bf16 = ("attention_mma", "attention_tc", "gemm_stream")
+
+    def __init__(self, w_in: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
+                 scale: float, eps: float, q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
+                 inv_freq: torch.Tensor | None = None, rot_dims: int = 0, window: int | None = None, chunk: int | None = None,
+                 gated: bool = True, padded_dim: int | None = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} KV heads")
+        rows = (n_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim + (n_heads if gated else 0)
+        if w_in.shape[0] != rows or w_o.shape[1] != n_heads * value_dim or w_o.shape[0] != w_in.shape[1]:
+            raise ValueError(f"attention weights do not fit: w_in {tuple(w_in.shape)}, w_o {tuple(w_o.shape)} for {n_heads}/"
+                             f"{n_kv_heads} heads of {head_dim} (values {value_dim}){' with a gate' if gated else ''}")
+        if rot_dims % 2 or not 0 <= rot_dims <= head_dim or (rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2)):
+            raise ValueError(f"{rot_dims} rotated entries of {head_dim} need {rot_dims // 2} frequencies")
+        for w in (q_norm_weight, k_norm_weight):
+            if w is not None and w.numel() != head_dim:
+                raise ValueError(f"a q/k norm weight has {w.numel()} entries for heads of {head_dim}")
+        self.w_in, self.w_o = w_in, w_o
+        self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim = n_heads, n_kv_heads, head_dim, value_dim
+        self.head_dim = max(head_dim, value_dim) if padded_dim is None else int(padded_dim)  # what the cache and the kernels see
+        if self.head_dim < max(head_dim, value_dim):
+            raise ValueError(f"padded size {self.head_dim} is below the key or value size")
+        f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
+        self.q_norm_weight, self.k_norm_weight, self.inv_freq = f32(q_norm_weight), f32(k_norm_weight), f32(inv_freq)
+        self.rot_dims, self.eps, self.gated = int(rot_dims), float(eps), gated
+        self.chunk, self.window, self.scale = chunk, window, float(scale)
+        self.position, self.qk_norm_eps = None, None
+
+    @staticmethod
+    def padded_size(head_dim: int, value_dim: int, dtype: torch.dtype) -> int:
+        """The common size of keys and values in the cache: with bfloat16 the next size that the tensor-core
+        attention kernels are built for, if there is one; else the larger of the two."""
+        d = max(head_dim, value_dim)
+        if dtype == torch.bfloat16:
+            for size in PagedAttention.MMA_HEAD_SIZES:
+                if d <= size:
+                    return size
+        return d
+
+    def sub_parts(self):
+        return ()
+
+    def core(self, ctx: StepContext, h, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
+        Hq, Hkv, dk, dv = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
+        n = proj.data.shape[-2]
+        q = torch.empty((n, Hq, self.head_dim), dtype=ctx.runtime.dtype, device=out.device)
+        with scope("rope"):
+            K.rope_half_kv_store(K.rows_view(proj.data, proj.splits, col), Hq * dk, (Hq + Hkv) * dk, q,
+                                 cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
+                                 ctx.req_of_token, ctx.positions, self.q_norm_weight, self.k_norm_weight, self.eps,
+                                 self.inv_freq, self.rot_dims, Hq, Hkv, dk, dv, ctx.status)
+        attn = torch.empty_like(q)
+        with scope("attention"):
+            self.attend(ctx, q, cache, attn, 0.0, 1.0)
+            gate = K.rows_view(proj.data, proj.splits, col + (Hq + Hkv) * dk + Hkv * dv) if self.gated else None
+            K.head_gate(attn, gate, mult, out, dv)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache):
+        return ProjectedMixer.forward(self, ctx, h, cache)
+
+
+register_part("mixer", "gated_paged_attention", GatedPagedAttention)

@@ -106,10 +106,28 @@ class PostNormed:
         return zero
 
 
-def as_rows(x: "torch.Tensor | Rows | RowSum | PostNormed | None") -> "Rows | None":
+@dataclasses.dataclass
+class Scaled:
+    """A delta that is still to be multiplied, channel by channel, by a vector before it is added: x += scale * rows
+    (a "layer scale").  A norm that can (``GroupRMSNorm``) does it in the same pass over the row as the residual sum
+    and its own norm; ``materialize()`` makes the plain [N, D] float32 tensor for a consumer that cannot."""
+
+    rows: Rows
+    scale: torch.Tensor  # float32 [D]
+
+    def materialize(self) -> torch.Tensor:
+        from ..kernels import api as K
+
+        n, d = self.rows.data.shape[-2], self.rows.data.shape[-1]
+        zero = torch.zeros((n, d), dtype=torch.float32, device=self.scale.device)
+        K.group_norm(zero, self.rows.data, self.rows.splits, None, self.scale, 1, 1.0, post_norm=False)
+        return zero
+
+
+def as_rows(x: "torch.Tensor | Rows | RowSum | PostNormed | Scaled | None") -> "Rows | None":
     if x is None or isinstance(x, Rows):
         return x
-    if isinstance(x, (RowSum, PostNormed)):
+    if isinstance(x, (RowSum, PostNormed, Scaled)):
         return Rows(x.materialize(), 1)
     return Rows(x, 1)
 
@@ -320,6 +338,42 @@ class Mixer(Part):
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> "torch.Tensor | Rows":
         """h: normed rows [N, D] in the runtime's dtype.  Returns delta [N, D] float32 (or Rows of partials)."""
         raise NotImplementedError
+
+
+class ProjectedMixer(Mixer):
+    """A mixer of the form  out = W_o core(W_in h):  one product into the rows ``core`` works on (float32 sums, possibly
+    still split-K partials), one product out of the rows it leaves.  A combinator (``ParallelMixers``) can then stack
+    the W_in of several such mixers that read the same h into one product, let each ``core`` fill its own column range
+    of one buffer, and send that through the W_o laid side by side: the sum of the mixers' outputs is then made by the
+    output product itself."""
+
+    w_in: torch.Tensor  # [in_features, D]
+    w_o: torch.Tensor  # [D, out_features]
+
+    @property
+    def in_features(self) -> int:
+        return self.w_in.shape[0]
+
+    @property
+    def out_features(self) -> int:
+        return self.w_o.shape[1]
+
+    def core(self, ctx: StepContext, h: torch.Tensor, proj: Rows, col: int, cache: LayerCache, out: torch.Tensor, mult: float) -> None:
+        """``proj``: float32 rows whose columns [col, col + in_features) are W_in h; ``h``: the mixer's input (for
+        small products of its own); writes ``mult`` times the rows for W_o into ``out`` [N, out_features] (maybe a
+        column range of wider rows)."""
+        raise NotImplementedError
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache):
+        from ..tracing import scope
+        from .linear import linear
+
+        with scope("qkv_matmul"):
+            proj = as_rows(linear(ctx, h, self.w_in, torch.float32, partials=True))
+        out = torch.empty((h.shape[0], self.out_features), dtype=ctx.runtime.dtype, device=h.device)
+        self.core(ctx, h, proj, 0, cache, out, 1.0)
+        with scope("projection"):
+            return linear(ctx, out, self.w_o, torch.float32, partials=True)
 
 
 class FeedForward(Part):

@@ -36,6 +36,47 @@ class PreNormBlock(Block):
 register_part("block", "pre_norm", PreNormBlock)
 
 
+class ScaledPreNormBlock(Block):
+    """A pre-norm block whose sublayers' outputs are multiplied channel by channel by a vector each before they are
+    added:  x += scale1 * mixer(norm1(x));  x += scale2 * feed_forward(norm2(x)).  The feed-forward (with norm2 and
+    scale2) may be missing.  A sublayer's output goes on as a :class:`Scaled` delta: the scale, the residual sum and
+    the next norm are one kernel."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, scale1: torch.Tensor, norm2: Norm | None = None,
+                 feed_forward: FeedForward | None = None, scale2: torch.Tensor | None = None):
+        if (feed_forward is None) != (norm2 is None) or (feed_forward is None) != (scale2 is None):
+            raise ValueError("a feed-forward comes with its norm and its scale, or not at all")
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.scale1 = scale1.to(torch.float32).contiguous()
+        self.scale2 = None if scale2 is None else scale2.to(torch.float32).contiguous()
+
+    def sub_parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache):
+        from .base import Scaled, as_rows
+
+        dt = ctx.runtime.dtype
+        with scope("attn_pre_norm"):
+            if self.mixer.needs_f32_input:
+                _, h32, _ = self.norm1.forward(ctx, x, delta, out_dtype=None, want_f32=True)
+                y = self.mixer.forward(ctx, None, cache, h32=h32)
+            else:
+                h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
+                y = self.mixer.forward(ctx, h, cache)
+        pending = Scaled(as_rows(y), self.scale1)
+        if self.feed_forward is None:
+            return pending
+        with scope("attn_post_norm"):
+            h, h32, _ = self.norm2.forward(ctx, x, pending, out_dtype=dt, want_f32=self.feed_forward.needs_f32_input)
+        with scope("ffn"):
+            y = self.feed_forward.forward(ctx, h, h32, None)
+        return Scaled(as_rows(y), self.scale2)
+
+
+register_part("block", "scaled_pre_norm", ScaledPreNormBlock)
+
+
 class SandwichNormBlock(Block):
     """A block that norms each sublayer's input and its output, and scales what it adds:
 

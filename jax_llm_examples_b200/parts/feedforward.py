@@ -230,3 +230,79 @@ class DenseBiasedMLP(FeedForward):
 
 
 register_part("feed_forward", "dense_biased", DenseBiasedMLP)
+
+
+class SoftmaxRoutedMLPExperts(FeedForward):
+    """Experts of the form down(act(up h)) chosen by a biased router, their OUTPUTS weighted:
+
+        z = W_router h + b (float32);  the top-k experts by z;  weights = softmax over the chosen z only;
+        out = sum_j weight_j * expert_j(h)  (+ shared(h): an expert of the same form that takes every token).
+
+    ``w_router``: [E, D]; ``router_bias``: [E]; ``we_up``: [E, F, D]; ``we_down``: [E, D, F]; ``activation``: a name
+    of ``K.ACTIVATIONS``.  The tokens' rows are gathered in expert order (unscaled), both products run as grouped
+    products over that order, and the kernel that brings the rows back applies the weights and adds the shared expert."""
+
+    kernel_libraries = ("moe", "group_norm", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
+    needs_f32_input = True
+
+    def __init__(self, w_router: torch.Tensor, router_bias: torch.Tensor | None, we_up: torch.Tensor, we_down: torch.Tensor,
+                 top_k: int, activation: str = "relu2", shared: "DenseBiasedMLP | None" = None):
+        E = w_router.shape[0]
+        if we_up.shape[0] != E or we_down.shape[0] != E or we_up.shape[1] != we_down.shape[2] or we_up.shape[2] != we_down.shape[1] \
+                or w_router.shape[1] != we_down.shape[1] or (router_bias is not None and router_bias.numel() != E):
+            raise ValueError(f"expert weights do not fit: router {tuple(w_router.shape)}, up {tuple(we_up.shape)}, down {tuple(we_down.shape)}")
+        if not 1 <= top_k <= E:
+            raise ValueError(f"top-{top_k} of {E} experts")
+        if activation not in K.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(K.ACTIVATIONS)}")
+        self.w_router = w_router.to(torch.float32).contiguous()
+        self.router_bias = None if router_bias is None else router_bias.to(torch.float32).contiguous()
+        self.we_up, self.we_down = we_up.contiguous(), we_down.contiguous()
+        self.top_k, self.num_experts, self.activation, self.shared = top_k, E, activation, shared
+
+    def sub_parts(self):
+        return () if self.shared is None else (self.shared,)
+
+    def forward(self, ctx: StepContext, h, h32, routing=None):
+        rt = ctx.runtime
+        n, D = h32.shape
+        k, E, dev = self.top_k, self.num_experts, h32.device
+        topk_idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+        topk_w = torch.empty((n, k), dtype=torch.float32, device=dev)
+        K.router(h32, self.w_router, topk_idx, topk_w, bias=self.router_bias, weight_form="softmax_of_chosen")
+        if "record_routing" in ctx.scratch:
+            ctx.scratch["record_routing"].append(topk_idx)
+        with scope("moe_routed_expert"):
+            with scope("permute"):
+                offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+                sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
+                sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
+                tiles = None
+                if self.we_up.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16:
+                    tile_rows = K.gemm_stream_token_tile(group_rows_hint(n * k, E))
+                    tiles = (torch.empty(2 * (-(-n * k // tile_rows) + E), dtype=torch.int32, device=dev),
+                             torch.empty(1, dtype=torch.int32, device=dev))
+                    K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, E, ctx.status, 0, tile_rows, *tiles)
+                else:
+                    K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, E, ctx.status)
+                a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=dev)
+                K.permute_scale(h32, sorted_pair, None, a_sorted, k)
+            with scope("we_gate_up"):
+                up = as_rows(grouped_linear(ctx, a_sorted, self.we_up, offsets, torch.float32, partials=True, tiles=tiles))
+                act = torch.empty((n * k, self.we_up.shape[1]), dtype=rt.dtype, device=dev)
+                K.bias_act(up.data, act, None, None, self.activation, up.splits)
+            with scope("we_down"):
+                y = as_rows(grouped_linear(ctx, act, self.we_down, offsets, torch.float32, partials=True, tiles=tiles))
+        shared = None
+        if self.shared is not None:
+            with scope("moe_shared_expert"):
+                shared = as_rows(self.shared.forward(ctx, h, None))
+        delta = torch.empty((n, D), dtype=torch.float32, device=dev)
+        with scope("unpermute"):
+            K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
+                          1 if shared is None else shared.splits, y.splits, -1, pair_weights=topk_w)
+        return delta
+
+
+register_part("feed_forward", "softmax_routed_mlp", SoftmaxRoutedMLPExperts)

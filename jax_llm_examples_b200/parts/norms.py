@@ -92,10 +92,15 @@ class GroupRMSNorm(Norm):
 
 def add_to_residual(x: torch.Tensor, delta, *, pre_weight=None, pre_groups: int = 1, pre_norm: bool = True, eps: float = 1e-6,
                     out=None, out32=None, row_index=None) -> None:
-    """x += delta, whatever form the pending delta has (None, a tensor, split-K partials, a :class:`PostNormed`),
+    """x += delta, whatever form the pending delta has (None, a tensor, split-K partials, a :class:`PostNormed`, a
+    :class:`Scaled`),
     and, in the same pass, out / out32 = the group norm of the new x (``pre_norm`` False: the new x itself)."""
-    from .base import PostNormed
+    from .base import PostNormed, Scaled
 
+    if isinstance(delta, Scaled):  # x += scale * delta, channel by channel, in the same pass
+        K.group_norm(x, delta.rows.data, delta.rows.splits, None, delta.scale, 1, 1.0, pre_weight, pre_groups, pre_norm, eps,
+                     out, out32, row_index, post_norm=False)
+        return
     if isinstance(delta, PostNormed):
         if abs(delta.eps - eps) > 0:
             # one kernel takes one eps: norm the delta on its own first

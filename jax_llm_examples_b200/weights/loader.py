@@ -26,7 +26,7 @@ import torch
 @dataclasses.dataclass(frozen=True)
 class TensorSpec:
     name: str
-    shape: tuple[int, ...]
+    shape: tuple[int, ...]  # an entry of -1: a size that only the stored tensor gives (any size fits)
     init: str = "normal"  # "normal": N(0, std); "norm": 1 + N(0, norm_noise); "bias": N(0, 1/4); "unit": in (0, 1)
     optional: bool = False
 
@@ -44,6 +44,10 @@ class WeightError(ValueError):
         if wrong:
             lines.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(wrong))
         super().__init__("\n".join(lines))
+
+
+def shape_fits(found: tuple[int, ...], spec: tuple[int, ...]) -> bool:
+    return len(found) == len(spec) and all(e == -1 or e == f for f, e in zip(found, spec))
 
 
 def _shard_files(model_dir: Path) -> list[Path]:
@@ -101,7 +105,7 @@ def load_tensors(
                     unexpected.append(f"{file_name} (given twice)")
                     continue
                 shape = tuple(f.get_slice(file_name).get_shape())
-                if shape != tuple(specs[name].shape):
+                if not shape_fits(shape, tuple(specs[name].shape)):
                     wrong.append(f"{file_name}: expected {list(specs[name].shape)}, found {list(shape)}")
                     found[name] = None  # type: ignore[assignment]
                     continue
@@ -119,7 +123,7 @@ def check_tensors(tensors: Mapping[str, torch.Tensor], specs: Mapping[str, Tenso
     wrong = [
         f"{n}: expected {list(specs[n].shape)}, found {list(t.shape)}"
         for n, t in tensors.items()
-        if n in specs and tuple(t.shape) != tuple(specs[n].shape)
+        if n in specs and not shape_fits(tuple(t.shape), tuple(specs[n].shape))
     ]
     if missing or unexpected or wrong:
         raise WeightError(where, missing, unexpected, wrong)

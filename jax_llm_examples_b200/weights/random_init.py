@@ -31,6 +31,9 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device: str |
     g.manual_seed(_tensor_seed(seed, spec.name))
     n = 1
     for s in spec.shape:
+        if s < 0:
+            raise ValueError(f"tensor {spec.name}: a size that only a stored tensor gives cannot be drawn at random "
+                             "(the configuration must name it)")
         n *= s
     if n <= (1 << 28):
         t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
