@@ -9,6 +9,7 @@
 //
 //   token_shift_blend  rows m of [M, N, D]: h + (h_prev - h) * mu_m, h_prev the request's previous token (its state
 //                      [D] across steps, zeros at the start); the step's last h of a request becomes its state.
+//                      It can also write the row offsets m * N of the blends (groups of a grouped product).
 //   decay_prep         q (scaled), k, v and the decay d of every token and head from projected rows (split-K partials
 //                      are added on the way); d = exp(-exp(z + b)) or sigmoid(z + b)^(1/tau).
 //   decay_scan         the recurrence over each request's tokens, in order; the state lives in registers.
@@ -40,10 +41,13 @@ __device__ __forceinline__ float rows_at(const RowsView& v, size_t row, int col)
 template <typename T>
 __global__ void token_shift_blend_kernel(const float* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
                                          const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
-                                         const int* __restrict__ req_of_token, T* __restrict__ out, int N, int R, int D, int M) {
+                                         const int* __restrict__ req_of_token, T* __restrict__ out, int N, int R, int D, int M,
+                                         int* __restrict__ group_offsets) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
   pdl_wait();
+  // the row offsets m * N of the M blends in the stacked output, for a grouped product over them
+  if (group_offsets && blockIdx.x == 0 && (int)threadIdx.x <= M) group_offsets[threadIdx.x] = threadIdx.x * N;
   int n;
   const float* prev;
   float* st = nullptr;
@@ -71,13 +75,13 @@ __global__ void token_shift_blend_kernel(const float* __restrict__ h, const floa
 
 JLX_API int jlx_token_shift_blend(const float* h, const float* mu, float* state, const int* cu_q, const int* slot_ids,
                                   const int* req_of_token, void* out, int out_dtype, int N, int R, int D, int M,
-                                  cudaStream_t stream) {
-  JLX_REQUIRE(N >= 0 && R >= 0 && D > 0 && M >= 1, "token_shift_blend: bad sizes N=%d R=%d D=%d M=%d", N, R, D, M);
+                                  int* group_offsets, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && R >= 0 && D > 0 && M >= 1 && M < 64, "token_shift_blend: bad sizes N=%d R=%d D=%d M=%d", N, R, D, M);
   if (N == 0) return 0;
   const int threads = D >= 1024 ? 256 : 128;
   JLX_DISPATCH_DTYPE(out_dtype, T, {
     JLX_CUDA(jlx_launch_pdl(token_shift_blend_kernel<T>, dim3(R + N), dim3(threads), 0, stream, h, mu, state, cu_q, slot_ids,
-                            req_of_token, (T*)out, N, R, D, M));
+                            req_of_token, (T*)out, N, R, D, M, group_offsets));
   });
   JLX_LAUNCH_CHECK("token_shift_blend");
   return 0;

@@ -445,21 +445,23 @@ def rows_view(data: torch.Tensor, splits: int = 1, col: int = 0, row: int = 0) -
     sp, stride = _splits(data, splits)
     v = _RowsView()
     v.p, v.split_stride, v.ld, v.splits = data.data_ptr() + 4 * (row * F + col), stride, F, sp
+    v.keep = data  # the view holds an address: the rows must live as long as it does
     return v
 
 
 def token_shift_blend(h32: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor,
-                      req_of_token: torch.Tensor, out: torch.Tensor) -> None:
+                      req_of_token: torch.Tensor, out: torch.Tensor, group_offsets: torch.Tensor | None = None) -> None:
     """out[m, n] = h[n] + (h_prev[n] - h[n]) * mu[m], h_prev the request's previous token: the row before, or for a
     step's first token of a request its state (float32 [slots, D], zeros at the start), which then becomes the
-    step's last row of the request.  h32: float32 [N, D]; mu: float32 [M, D]; out: [M, N, D]."""
+    step's last row of the request.  h32: float32 [N, D]; mu: float32 [M, D]; out: [M, N, D].  ``group_offsets`` (int32
+    [M + 1]) gets the row offsets m * N of the blends in ``out`` seen as [M N, D]."""
     _contig(h32, mu, state, out)
     N, D = h32.shape
     M = mu.shape[0]
     if any(t.dtype != torch.float32 for t in (h32, mu, state)) or tuple(out.shape) != (M, N, D) or tuple(state.shape[1:]) != (D,):
         raise KernelError("token_shift_blend: float32 rows, blend weights and state [slots, D] and out [M, N, D] are needed")
     _run("decay_scan", "jlx_token_shift_blend", _ptr(h32), _ptr(mu), _ptr(state), _ptr(cu_q), _ptr(slot_ids), _ptr(req_of_token),
-         _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(slot_ids.numel()), c_int(D), c_int(M), _stream())
+         _ptr(out), c_int(code(out.dtype)), c_int(N), c_int(slot_ids.numel()), c_int(D), c_int(M), _ptr(group_offsets), _stream())
 
 
 DECAY_FORMS = {"double_exp": 0, "sigmoid_power": 1}  # csrc/decay_scan.cu

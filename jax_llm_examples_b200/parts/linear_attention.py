@@ -105,17 +105,9 @@ class TimeMixWKV(Mixer):
         self.mu, self.w0, self.bonus, self.norm_weight = f32(mu), f32(w0), f32(bonus).view(heads, dim), f32(norm_weight)
         self.w_rkvg, self.w_w1, self.w_w2, self.w_o = w_rkvg.contiguous(), w_w1.contiguous(), w_w2.contiguous(), w_o
         self.heads, self.dim, self.eps, self.width = heads, dim, float(eps), D
-        self._offsets: dict[int, torch.Tensor] = {}
 
     def state_needs(self):
         return (StateNeed((self.width,), torch.float32), StateNeed((self.heads, self.dim, self.dim), torch.float32))
-
-    def _group_offsets(self, n: int, device) -> torch.Tensor:
-        """Row offsets of the four projections' groups over the stacked blends [4 N, D] (made once per step size)."""
-        t = self._offsets.get(n)
-        if t is None:
-            t = self._offsets[n] = (torch.arange(5, dtype=torch.int32) * n).to(device)
-        return t
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, h32: torch.Tensor | None = None):
         n, D = h32.shape
@@ -123,10 +115,11 @@ class TimeMixWKV(Mixer):
         dt = ctx.runtime.dtype
         shift_state, S = cache.states
         blends = torch.empty((5, n, D), dtype=dt, device=h32.device)
-        K.token_shift_blend(h32, self.mu, shift_state, ctx.cu_q, ctx.slot_ids, ctx.req_of_token, blends)
+        offsets = torch.empty(6, dtype=torch.int32, device=h32.device)  # row offsets of the blends: the groups of the product below
+        K.token_shift_blend(h32, self.mu, shift_state, ctx.cu_q, ctx.slot_ids, ctx.req_of_token, blends, offsets)
         with scope("qkv_matmul"):
             # the four projections, each of its own blend, as one grouped product over the stacked rows
-            rkvg = as_rows(grouped_linear(ctx, blends[:4].view(4 * n, D), self.w_rkvg, self._group_offsets(n, h32.device),
+            rkvg = as_rows(grouped_linear(ctx, blends[:4].view(4 * n, D), self.w_rkvg, offsets,
                                           torch.float32, partials=True, largest_group=n))
             w1 = as_rows(linear(ctx, blends[4], self.w_w1, torch.float32, partials=True))
             lora = torch.empty((n, self.w_w1.shape[0]), dtype=dt, device=h32.device)
