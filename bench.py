@@ -472,12 +472,14 @@ def run_compare(args) -> dict:
     """--compare tebivik: prefill and decode throughput of Tebivik at layer sizes of real models beside the closest
     model the framework had before (a dense Llama-4-style decoder of the same width, depth and head count), random
     weights, one GPU; with each model's device time by kernel for one prompt step and one decode step, and for the
-    kernels that differ between the two the fraction of the measured roofline that they reach."""
+    kernels that differ between the two the fraction of the measured roofline that they reach.
+    --compare makisun: the same for Makisun beside Tebivik (the closest: recurrences and attention in turn, the same
+    norm kernels) at equal width, depth, head count and feed-forward size, and Makisun with routed experts."""
     import torch
 
     import jax_llm_examples_b200 as J
     from jax_llm_examples_b200 import tracing
-    from jax_llm_examples_b200.config.presets import dense_llama_sized, tebivik_sized
+    from jax_llm_examples_b200.config.presets import dense_llama_sized, makisun_sized, tebivik_sized
 
     peaks, peak_src = _peaks()
     hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
@@ -487,7 +489,8 @@ def run_compare(args) -> dict:
     sizes = [(2048, 8, 16, 8192), (4096, 8, 32, 14336)]
     if args.layers:
         sizes = [(w, args.layers, h, f) for w, _, h, f in sizes]
-    out = {"metric": "prefill and decode throughput, Tebivik beside a dense Llama-4-style decoder", "unit": "tok/s", "n_gpus": 1,
+    what = {"tebivik": "Tebivik beside a dense Llama-4-style decoder", "makisun": "Makisun beside Tebivik"}[args.compare]
+    out = {"metric": "prefill and decode throughput, " + what, "unit": "tok/s", "n_gpus": 1,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": peaks, "peaks_source": peak_src,
            "config": {"prefill_tokens": P, "decode_batch": B, "decode_context": C, "l2": "a 256 MiB buffer is written between timed steps"},
            "sizes": []}
@@ -552,7 +555,40 @@ def run_compare(args) -> dict:
 
     clocks = ClockSampler()
     clocks.start()
-    for width, layers, heads, ff in sizes:
+    for width, layers, heads, ff in sizes if args.compare == "makisun" else ():
+        m, t = measure(makisun_sized(width, layers, heads, ff)), measure(tebivik_sized(width, layers, heads, ff))
+        routed = measure(makisun_sized(width, layers, heads, ff, experts=16))
+        par, rec = (layers + 1) // 2, layers // 2  # Makisun's layers: attention beside gated linear attention / time mix
+        t_runs = layers + layers // 2  # the first half of Tebivik's layers runs twice
+        t_att = sum(1 for i in range(layers) if i % 2 == 0) + sum(1 for i in range(layers // 2) if i % 2 == 0)
+        t_rec = t_runs - t_att
+        dh, hkv, window, rank, dr = 128, max(heads // 4, 1), 1024, 512, 64
+        state = 128 * 128 * 8  # a head's state read and written, float32
+        scan_state = (rec * heads + par * max(heads // 2, 1)) * state
+        scan_rows = (rec * heads + par * max(heads // 2, 1)) * 128 * 5 * 4  # q, k, decay, v in and o out per token and head
+        seen = sum(min(i + 1, window) for i in range(P))  # keys that a prompt's queries see through the window
+        roof = {
+            "decode": {
+                "makisun decay_scan": frac(m["decode_kernels_ms"].get("jlx_decay_scan", 0), B * scan_state),
+                "tebivik hgrn2_scan": frac(t["decode_kernels_ms"].get("jlx_hgrn2_scan", 0), t_rec * B * heads * state),
+                "makisun attention_decode": frac(m["decode_kernels_ms"].get("jlx_attention_decode", 0), par * B * min(C, window) * 2 * hkv * dh * 2),
+                "tebivik attention_latent": frac(t["decode_kernels_ms"].get("jlx_attention_latent", 0), t_att * B * C * (rank + dr) * 2),
+                "makisun group_norm": frac(m["decode_kernels_ms"].get("jlx_group_norm", 0), (2 * layers + 1) * B * width * 14),
+                "tebivik group_norm": frac(t["decode_kernels_ms"].get("jlx_group_norm", 0), (2 * t_runs + 1) * B * width * 14),
+            },
+            "prefill": {
+                "makisun decay_scan": frac(m["prefill_kernels_ms"].get("jlx_decay_scan", 0), P * scan_rows),
+                "tebivik hgrn2_scan": frac(t["prefill_kernels_ms"].get("jlx_hgrn2_scan", 0), t_rec * P * (2 * heads * 128 + heads * 128) * 4, 0),
+                "makisun attention_prefill_tc": frac(m["prefill_kernels_ms"].get("jlx_attention_prefill_tc", 0), 0, par * heads * seen * 4 * dh),
+                "tebivik causal_sink_softmax": frac(t["prefill_kernels_ms"].get("jlx_causal_sink_softmax", 0),
+                                                    t_att * heads * sum(min(512, P - t0) * min(P, t0 + 512) for t0 in range(0, P, 512)) * 6),
+                "makisun group_norm": frac(m["prefill_kernels_ms"].get("jlx_group_norm", 0), (2 * layers + 1) * P * width * 14),
+                "tebivik group_norm": frac(t["prefill_kernels_ms"].get("jlx_group_norm", 0), (2 * t_runs + 1) * P * width * 14),
+            },
+        }
+        out["sizes"].append({"width": width, "layers": layers, "layer_runs_tebivik": t_runs, "heads": heads, "ff": ff, "makisun": m,
+                             "makisun_16_experts": routed, "tebivik": t, "fraction_of_measured_roofline": roof})
+    for width, layers, heads, ff in sizes if args.compare == "tebivik" else ():
         t_cfg, l_cfg = tebivik_sized(width, layers, heads, ff), dense_llama_sized(width, layers, heads, ff)
         t, l = measure(t_cfg), measure(l_cfg)
         runs = layers + layers // 2  # the first half of Tebivik's layers runs twice
@@ -602,7 +638,7 @@ def main() -> int:
     ap.add_argument("--long-tokens", type=int, default=32768)
     ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
-    ap.add_argument("--compare", default=None, choices=["tebivik"],
+    ap.add_argument("--compare", default=None, choices=["tebivik", "makisun"],
                     help="instead of the benchmark: throughput of this architecture at real layer sizes beside the closest "
                     "model the framework had before (with --prefill-tokens, --batch, --context up to 4096, --layers)")
     args = ap.parse_args()

@@ -94,6 +94,37 @@ PRESETS["tebivik_tiny"] = {
         {"type": "hgrn2", "mixer": {"heads": 4, "dim": 8, "vdim": 16}, "mlp": None},
     ],
 }
+def makisun_sized(width: int, layers: int, heads: int, ff: int, vocab: int = 32768, experts: int = 0) -> dict[str, Any]:
+    """A Makisun configuration at the layer sizes of a real model: layers of windowed attention (head size 128, four
+    query heads per key head, a window of 1024, half the head rotated) beside gated linear attention (half as many heads,
+    state 128 x 128), and time-mix layers (state 128 x 128 per head) in turn; a dense feed-forward in every layer, or
+    with ``experts`` > 0 a mixture (top 2, each expert and the shared one a quarter of ``ff``) in every second layer."""
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": experts, "top": 2}, "shared": {"ff": ff // 4}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "mask": {"size": 1024},
+                              "rot": {"base": 10000.0, "dims": 64}, "scale": 128 ** -0.5},
+                     "right": {"heads": max(heads // 2, 1), "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64},
+                     "left_scale": 1.0, "right_scale": 1.0}}
+    rec = {"type": "wkv", "mixer": {"heads": heads, "dim": 128, "decay_rank": 64}}
+    return {"architecture": "Makisun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [dict(par if i % 2 == 0 else rec, mlp=routed if experts and i % 2 else dense) for i in range(layers)]}
+
+
+PRESETS["makisun_tiny"] = {
+    "architecture": "Makisun", "vocab": 256, "width": 64, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 16, "decay_rank": 8},
+         "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 4, "top": 2}, "shared": {"ff": 16}}},
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"left": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "mask": {"size": 24}, "rot": {"base": 10000.0, "dims": 8},
+                            "scale": 0.25},
+                   "right": {"heads": 2, "dim": 8, "vdim": 16, "tau": 4.0, "decay_rank": 8}, "left_scale": 0.75, "right_scale": 1.25}},
+        {"type": "wkv", "mixer": {"heads": 4, "dim": 8, "decay_rank": 8}, "mlp": None},
+    ],
+}
+PRESETS["makisun_2k"] = makisun_sized(2048, 8, 16, 8192)
+PRESETS["makisun_4k"] = makisun_sized(4096, 8, 32, 14336)
 PRESETS["tebivik_2k"] = tebivik_sized(2048, 8, 16, 8192)
 PRESETS["tebivik_4k"] = tebivik_sized(4096, 8, 32, 14336)
 PRESETS["scout8_long"] = {**PRESETS["scout16"], "num_hidden_layers": 8, "no_rope_layers": _every_nth_nope(8, 4)}

@@ -133,9 +133,20 @@ JLX_API int jlx_decay_prep(const RowsView* q, const RowsView* k, const RowsView*
 // ------------------------------------------------------------------------------------------------ the recurrence
 // One block per (request, head, slice of 32 value columns).  Lane = a value column; warp w keeps rows [w NR, (w+1) NR)
 // of S for that column in registers.  The tokens' q, k, d rows and v slice come through shared memory SCAN_TB tokens
-// at a time; between two barriers a warp walks those tokens (o does not feed back into S) and leaves its part of each
-// o; the parts are added in warp order.
+// at a time, two buffers taking turns: while a group of tokens is walked, asynchronous copies bring the next.  Between
+// two barriers a warp walks a group (o does not feed back into S), reading its rows' q, k, d four at a time, and leaves
+// its part of each o; the parts are added in warp order.  A token's sums run in the same order wherever it stands in a
+// step, so portions give bit for bit what whole prompts give.
 #define SCAN_TB 16
+
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int NR, bool READ_AFTER>
 __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ d,
@@ -144,14 +155,11 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
                                   int H, int dk, int dv) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
   const int dkp = W * NR;
-  float* qs = smem;                  // [SCAN_TB][dkp]
-  float* ks = qs + SCAN_TB * dkp;
-  float* ds = ks + SCAN_TB * dkp;
-  float* vs = ds + SCAN_TB * dkp;    // [SCAN_TB][32]
-  float* part = vs + SCAN_TB * 32;   // [SCAN_TB][W][32]
+  const int stage_floats = 3 * SCAN_TB * dkp + SCAN_TB * 32;  // [q | k | d][SCAN_TB][dkp], v [SCAN_TB][32]
+  float* part = smem + 2 * stage_floats;                     // [SCAN_TB][W][32]
   const int r = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * 32;
   const int j = j0 + lane;
   const bool col = j < dv;
@@ -159,6 +167,18 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
   float uu[NR];
 #pragma unroll
   for (int ii = 0; ii < NR; ++ii) uu[ii] = (!READ_AFTER && u && i0 + ii < dk) ? u[hd * dk + i0 + ii] : 0.f;
+  // what no copy ever writes: rows beyond dk (q = k = 0, d = 1) and value columns beyond dv (0)
+  for (int b = 0; b < 2; ++b) {
+    float* st = smem + b * stage_floats;
+    for (int idx = threadIdx.x; idx < SCAN_TB * dkp; idx += blockDim.x)
+      if (idx % dkp >= dk) {
+        st[idx] = 0.f;
+        st[SCAN_TB * dkp + idx] = 0.f;
+        st[2 * SCAN_TB * dkp + idx] = 1.f;
+      }
+    for (int idx = threadIdx.x; idx < SCAN_TB * 32; idx += blockDim.x)
+      if (j0 + (idx & 31) >= dv) st[3 * SCAN_TB * dkp + idx] = 0.f;
+  }
   pdl_wait();
   const int n0 = cu_q[r], n1 = cu_q[r + 1];
   if (n1 <= n0) return;
@@ -167,53 +187,89 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
 #pragma unroll
   for (int ii = 0; ii < NR; ++ii) s[ii] = (col && i0 + ii < dk) ? S[(size_t)(i0 + ii) * dv + j] : 0.f;
 
-  auto stage = [&](int t0) {
+  // 16-byte copies where every row starts on a 16-byte boundary
+  const bool vec = (dk & 3) == 0 && (dv & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)d | (uintptr_t)v) & 15) == 0);
+  auto stage = [&](int t0, int b) {  // asynchronous copies of the group's rows into buffer b
+    float* st = smem + b * stage_floats;
     const int cnt = min(SCAN_TB, n1 - t0);
-    for (int idx = threadIdx.x; idx < cnt * dkp; idx += blockDim.x) {
-      const int tt = idx / dkp, i = idx - tt * dkp;
+    if (vec) {
+      const int dk4 = dk >> 2, nv4 = min(32, dv - j0) >> 2;
+      for (int idx = threadIdx.x; idx < cnt * dk4; idx += blockDim.x) {
+        const int tt = idx / dk4, i = (idx - tt * dk4) << 2;
+        const size_t at = ((size_t)(t0 + tt) * H + hd) * dk + i;
+        float* dst = st + tt * dkp + i;
+        cp_async16(dst, q + at);
+        cp_async16(dst + SCAN_TB * dkp, k + at);
+        cp_async16(dst + 2 * SCAN_TB * dkp, d + at);
+      }
+      for (int idx = threadIdx.x; idx < cnt * nv4; idx += blockDim.x) {
+        const int tt = idx / nv4, l = (idx - tt * nv4) << 2;
+        cp_async16(st + 3 * SCAN_TB * dkp + tt * 32 + l, v + ((size_t)(t0 + tt) * H + hd) * dv + j0 + l);
+      }
+      cp_async_commit();
+      return;
+    }
+    for (int idx = threadIdx.x; idx < cnt * dk; idx += blockDim.x) {
+      const int tt = idx / dk, i = idx - tt * dk;
       const size_t at = ((size_t)(t0 + tt) * H + hd) * dk + i;
-      const bool in = i < dk;
-      qs[idx] = in ? q[at] : 0.f;
-      ks[idx] = in ? k[at] : 0.f;
-      ds[idx] = in ? d[at] : 1.f;
+      float* dst = st + tt * dkp + i;
+      cp_async4(dst, q + at);
+      cp_async4(dst + SCAN_TB * dkp, k + at);
+      cp_async4(dst + 2 * SCAN_TB * dkp, d + at);
     }
-    for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
-      const int tt = idx >> 5, l = idx & 31;
-      vs[idx] = j0 + l < dv ? v[((size_t)(t0 + tt) * H + hd) * dv + j0 + l] : 0.f;
+    const int nv = min(32, dv - j0);
+    for (int idx = threadIdx.x; idx < cnt * nv; idx += blockDim.x) {
+      const int tt = idx / nv, l = idx - tt * nv;
+      cp_async4(st + 3 * SCAN_TB * dkp + tt * 32 + l, v + ((size_t)(t0 + tt) * H + hd) * dv + j0 + l);
     }
+    cp_async_commit();
   };
 
-  stage(n0);
-  for (int t0 = n0; t0 < n1; t0 += SCAN_TB) {
+  stage(n0, 0);
+  int b = 0;
+  for (int t0 = n0; t0 < n1; t0 += SCAN_TB, b ^= 1) {
     const int cnt = min(SCAN_TB, n1 - t0);
-    __syncthreads();  // the staged tokens are there; the parts of the tokens before are consumed
+    const bool more = t0 + SCAN_TB < n1;
+    if (more) {
+      stage(t0 + SCAN_TB, b ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();  // this group's rows are there; the parts of the group before are consumed
+    const float* st = smem + b * stage_floats;
     for (int tt = 0; tt < cnt; ++tt) {
-      const float vj = vs[tt * 32 + lane];
-      const float* qt = qs + tt * dkp + i0;
-      const float* kt = ks + tt * dkp + i0;
-      const float* dt = ds + tt * dkp + i0;
-      float acc = 0.f;
+      const float vj = st[3 * SCAN_TB * dkp + tt * 32 + lane];
+      const float4* qt = reinterpret_cast<const float4*>(st + tt * dkp + i0);
+      const float4* kt = reinterpret_cast<const float4*>(st + SCAN_TB * dkp + tt * dkp + i0);
+      const float4* dt = reinterpret_cast<const float4*>(st + 2 * SCAN_TB * dkp + tt * dkp + i0);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ii = 0; ii < NR; ++ii) {
-        const float kv = kt[ii] * vj;
-        if (READ_AFTER) {
-          s[ii] = fmaf(dt[ii], s[ii], kv);
-          acc = fmaf(qt[ii], s[ii], acc);
-        } else {
-          acc = fmaf(qt[ii], fmaf(uu[ii], kv, s[ii]), acc);
-          s[ii] = fmaf(dt[ii], s[ii], kv);
+      for (int i4 = 0; i4 < NR / 4; ++i4) {
+        const float4 q4 = qt[i4], k4 = kt[i4], d4 = dt[i4];
+        const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int ii = 4 * i4 + c;
+          const float kv = kk[c] * vj;
+          if (READ_AFTER) {
+            s[ii] = fmaf(dd[c], s[ii], kv);
+            acc[c] = fmaf(qq[c], s[ii], acc[c]);
+          } else {
+            acc[c] = fmaf(qq[c], fmaf(uu[ii], kv, s[ii]), acc[c]);
+            s[ii] = fmaf(dd[c], s[ii], kv);
+          }
         }
       }
-      part[(tt * W + warp) * 32 + lane] = acc;
+      part[(tt * W + warp) * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
-    __syncthreads();  // the parts are there; the staged tokens are consumed
+    __syncthreads();  // the parts are there; this group's rows are consumed
     for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
       const int tt = idx >> 5, l = idx & 31;
       float sum = 0.f;
       for (int w = 0; w < W; ++w) sum += part[(tt * W + w) * 32 + l];
       if (j0 + l < dv) o[((size_t)(t0 + tt) * H + hd) * dv + j0 + l] = sum;
     }
-    if (t0 + SCAN_TB < n1) stage(t0 + SCAN_TB);
   }
 #pragma unroll
   for (int ii = 0; ii < NR; ++ii)
@@ -224,7 +280,7 @@ template <int NR, bool READ_AFTER>
 static int launch_decay_scan(const float* q, const float* k, const float* d, const float* v, const float* u, float* state,
                              const int* cu_q, const int* slot_ids, float* o, int R, int H, int dk, int dv, cudaStream_t stream) {
   const int W = (dk + NR - 1) / NR;
-  const size_t smem = sizeof(float) * ((size_t)3 * SCAN_TB * W * NR + SCAN_TB * 32 + (size_t)SCAN_TB * W * 32);
+  const size_t smem = sizeof(float) * (2 * ((size_t)3 * SCAN_TB * W * NR + SCAN_TB * 32) + (size_t)SCAN_TB * W * 32);
   if (smem > 48 * 1024)
     JLX_CUDA(cudaFuncSetAttribute(decay_scan_kernel<NR, READ_AFTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   JLX_CUDA(jlx_launch_pdl(decay_scan_kernel<NR, READ_AFTER>, dim3(R, H, (dv + 31) / 32), dim3(W * 32), smem, stream, q, k, d, v, u,

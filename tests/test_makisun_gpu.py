@@ -546,9 +546,11 @@ def test_greedy_generation_through_the_scheduler(folders, name, dtype):
         MH.greedy_checked(folders[name], p, g, dtype)
 
 
-def test_command_line_generates_from_a_folder(folders, capsys):
+def test_command_line_generates_from_a_preset_and_from_a_folder(folders, capsys):
     from jax_llm_examples_b200.main import main
 
+    assert main(["--preset", "makisun_tiny", "--random-prompts", "2", "--prompt-len", "9", "--max-new-tokens", "4"]) == 0
+    assert capsys.readouterr().out.count("-" * 80) == 2
     assert main(["--model", str(folders["recurrent"]), "--dtype", "float32", "--prompt-ids", "1,2,3,4,5", "--max-new-tokens", "5",
                  "--page-size", "16"]) == 0
     ids = [int(t) for t in capsys.readouterr().out.splitlines()[1].split()]
