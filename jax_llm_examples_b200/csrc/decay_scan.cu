@@ -148,25 +148,32 @@ __device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int NR, bool READ_AFTER>
+// G: row groups within a warp.  With G = 1 a lane is one of 32 value columns and holds NR rows; with G = 2 or 4 a block
+// serves 16 or 8 columns, and a warp's lanes split its NR rows between them (NR / G each), their parts of o meeting in
+// shuffles.  More, lighter blocks: a model with few heads still fills the GPU with one request.  G is chosen from the
+// model's sizes alone (never from the batch), so a token's sums do not change with what else is in the step.
+template <int NR, int G, bool READ_AFTER>
 __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ d,
                                   const float* __restrict__ v, const float* __restrict__ u, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids, float* __restrict__ o,
                                   int H, int dk, int dv) {
   JLX_TL(TL_OTHER);
   pdl_launch_dependents_if_small();
+  constexpr int CW = 32 / G, RL = NR / G;
+  static_assert(RL >= 4 && RL % 4 == 0, "a lane reads its rows four at a time");
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int cl = lane % CW, rg = lane / CW;
   const int dkp = W * NR;
-  const int stage_floats = 3 * SCAN_TB * dkp + SCAN_TB * 32;  // [q | k | d][SCAN_TB][dkp], v [SCAN_TB][32]
-  float* part = smem + 2 * stage_floats;                     // [SCAN_TB][W][32]
-  const int r = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * 32;
-  const int j = j0 + lane;
+  const int stage_floats = 3 * SCAN_TB * dkp + SCAN_TB * 32;  // [q | k | d][SCAN_TB][dkp], v [SCAN_TB][32] (CW in use)
+  float* part = smem + 2 * stage_floats;                     // [SCAN_TB][W][CW]
+  const int r = blockIdx.x, hd = blockIdx.y, j0 = blockIdx.z * CW;
+  const int j = j0 + cl;
   const bool col = j < dv;
-  const int i0 = warp * NR;
-  float uu[NR];
+  const int i0 = warp * NR + rg * RL;
+  float uu[RL];
 #pragma unroll
-  for (int ii = 0; ii < NR; ++ii) uu[ii] = (!READ_AFTER && u && i0 + ii < dk) ? u[hd * dk + i0 + ii] : 0.f;
+  for (int ii = 0; ii < RL; ++ii) uu[ii] = (!READ_AFTER && u && i0 + ii < dk) ? u[hd * dk + i0 + ii] : 0.f;
   // what no copy ever writes: rows beyond dk (q = k = 0, d = 1) and value columns beyond dv (0)
   for (int b = 0; b < 2; ++b) {
     float* st = smem + b * stage_floats;
@@ -183,17 +190,18 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
   const int n0 = cu_q[r], n1 = cu_q[r + 1];
   if (n1 <= n0) return;
   float* S = state + ((size_t)slot_ids[r] * H + hd) * dk * dv;
-  float s[NR];
+  float s[RL];
 #pragma unroll
-  for (int ii = 0; ii < NR; ++ii) s[ii] = (col && i0 + ii < dk) ? S[(size_t)(i0 + ii) * dv + j] : 0.f;
+  for (int ii = 0; ii < RL; ++ii) s[ii] = (col && i0 + ii < dk) ? S[(size_t)(i0 + ii) * dv + j] : 0.f;
 
   // 16-byte copies where every row starts on a 16-byte boundary
   const bool vec = (dk & 3) == 0 && (dv & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)d | (uintptr_t)v) & 15) == 0);
+  const int nv = min(CW, dv - j0);
   auto stage = [&](int t0, int b) {  // asynchronous copies of the group's rows into buffer b
     float* st = smem + b * stage_floats;
     const int cnt = min(SCAN_TB, n1 - t0);
     if (vec) {
-      const int dk4 = dk >> 2, nv4 = min(32, dv - j0) >> 2;
+      const int dk4 = dk >> 2, nv4 = nv >> 2;
       for (int idx = threadIdx.x; idx < cnt * dk4; idx += blockDim.x) {
         const int tt = idx / dk4, i = (idx - tt * dk4) << 2;
         const size_t at = ((size_t)(t0 + tt) * H + hd) * dk + i;
@@ -217,7 +225,6 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
       cp_async4(dst + SCAN_TB * dkp, k + at);
       cp_async4(dst + 2 * SCAN_TB * dkp, d + at);
     }
-    const int nv = min(32, dv - j0);
     for (int idx = threadIdx.x; idx < cnt * nv; idx += blockDim.x) {
       const int tt = idx / nv, l = idx - tt * nv;
       cp_async4(st + 3 * SCAN_TB * dkp + tt * 32 + l, v + ((size_t)(t0 + tt) * H + hd) * dv + j0 + l);
@@ -238,14 +245,16 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
     }
     __syncthreads();  // this group's rows are there; the parts of the group before are consumed
     const float* st = smem + b * stage_floats;
+    // unrolled, so that the next tokens' reads from shared memory are in flight while a token's sums are made
+#pragma unroll 4
     for (int tt = 0; tt < cnt; ++tt) {
-      const float vj = st[3 * SCAN_TB * dkp + tt * 32 + lane];
+      const float vj = st[3 * SCAN_TB * dkp + tt * 32 + cl];
       const float4* qt = reinterpret_cast<const float4*>(st + tt * dkp + i0);
       const float4* kt = reinterpret_cast<const float4*>(st + SCAN_TB * dkp + tt * dkp + i0);
       const float4* dt = reinterpret_cast<const float4*>(st + 2 * SCAN_TB * dkp + tt * dkp + i0);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i4 = 0; i4 < NR / 4; ++i4) {
+      for (int i4 = 0; i4 < RL / 4; ++i4) {
         const float4 q4 = qt[i4], k4 = kt[i4], d4 = dt[i4];
         const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
@@ -261,32 +270,43 @@ __global__ void decay_scan_kernel(const float* __restrict__ q, const float* __re
           }
         }
       }
-      part[(tt * W + warp) * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      if (G == 4) total += __shfl_xor_sync(0xffffffffu, total, 8);
+      if (G >= 2) total += __shfl_xor_sync(0xffffffffu, total, 16);
+      if (rg == 0) part[(tt * W + warp) * CW + cl] = total;
     }
     __syncthreads();  // the parts are there; this group's rows are consumed
-    for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
-      const int tt = idx >> 5, l = idx & 31;
+    for (int idx = threadIdx.x; idx < cnt * CW; idx += blockDim.x) {
+      const int tt = idx / CW, l = idx % CW;
       float sum = 0.f;
-      for (int w = 0; w < W; ++w) sum += part[(tt * W + w) * 32 + l];
+      for (int w = 0; w < W; ++w) sum += part[(tt * W + w) * CW + l];
       if (j0 + l < dv) o[((size_t)(t0 + tt) * H + hd) * dv + j0 + l] = sum;
     }
   }
 #pragma unroll
-  for (int ii = 0; ii < NR; ++ii)
+  for (int ii = 0; ii < RL; ++ii)
     if (col && i0 + ii < dk) S[(size_t)(i0 + ii) * dv + j] = s[ii];
 }
 
-template <int NR, bool READ_AFTER>
+template <int NR, int G, bool READ_AFTER>
 static int launch_decay_scan(const float* q, const float* k, const float* d, const float* v, const float* u, float* state,
                              const int* cu_q, const int* slot_ids, float* o, int R, int H, int dk, int dv, cudaStream_t stream) {
-  const int W = (dk + NR - 1) / NR;
-  const size_t smem = sizeof(float) * (2 * ((size_t)3 * SCAN_TB * W * NR + SCAN_TB * 32) + (size_t)SCAN_TB * W * 32);
+  const int W = (dk + NR - 1) / NR, CW = 32 / G;
+  const size_t smem = sizeof(float) * (2 * ((size_t)3 * SCAN_TB * W * NR + SCAN_TB * 32) + (size_t)SCAN_TB * W * CW);
   if (smem > 48 * 1024)
-    JLX_CUDA(cudaFuncSetAttribute(decay_scan_kernel<NR, READ_AFTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  JLX_CUDA(jlx_launch_pdl(decay_scan_kernel<NR, READ_AFTER>, dim3(R, H, (dv + 31) / 32), dim3(W * 32), smem, stream, q, k, d, v, u,
-                          state, cu_q, slot_ids, o, H, dk, dv));
+    JLX_CUDA(cudaFuncSetAttribute(decay_scan_kernel<NR, G, READ_AFTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  JLX_CUDA(jlx_launch_pdl(decay_scan_kernel<NR, G, READ_AFTER>, dim3(R, H, (dv + CW - 1) / CW), dim3(W * 32), smem, stream, q, k, d, v,
+                          u, state, cu_q, slot_ids, o, H, dk, dv));
   JLX_LAUNCH_CHECK("decay_scan");
   return 0;
+}
+
+// Blocks that one request gives with G row groups per warp; enough of them (SCAN_FILL) fill the GPU.
+#define SCAN_FILL 128
+static int scan_row_groups(int H, int dv, int nr) {
+  if (H * ((dv + 31) / 32) >= SCAN_FILL || nr < 8) return 1;
+  if (H * ((dv + 15) / 16) >= SCAN_FILL || nr < 16) return 2;
+  return 4;
 }
 
 // q, k, d: float32 [N, H, dk]; v: [N, H, dv]; u: [H, dk] or null (only read before the update); state: [slots, H, dk, dv];
@@ -296,16 +316,27 @@ JLX_API int jlx_decay_scan(const float* q, const float* k, const float* d, const
                            cudaStream_t stream) {
   JLX_REQUIRE(R >= 0 && H > 0 && dk > 0 && dv > 0, "decay_scan: bad sizes R=%d H=%d dk=%d dv=%d", R, H, dk, dv);
   JLX_REQUIRE(dk <= 512, "decay_scan: %d key channels per head; up to 512 are supported", dk);
-  JLX_REQUIRE(H <= 65535 && (dv + 31) / 32 <= 65535, "decay_scan: too many heads or value columns");
+  JLX_REQUIRE(H <= 65535 && (dv + 7) / 8 <= 65535, "decay_scan: too many heads or value columns");
   if (R == 0) return 0;
-#define JLX_SCAN(NR)                                                                                                      \
-  return read_after ? launch_decay_scan<NR, true>(q, k, d, v, u, state, cu_q, slot_ids, o, R, H, dk, dv, stream)          \
-                    : launch_decay_scan<NR, false>(q, k, d, v, u, state, cu_q, slot_ids, o, R, H, dk, dv, stream)
-  if (dk <= 32) { JLX_SCAN(8); }
-  if (dk <= 128) { JLX_SCAN(16); }
-  if (dk <= 256) { JLX_SCAN(32); }
-  JLX_SCAN(64);
+#define JLX_SCAN_ARGS q, k, d, v, u, state, cu_q, slot_ids, o, R, H, dk, dv, stream
+#define JLX_SCAN(NR, G) return read_after ? launch_decay_scan<NR, G, true>(JLX_SCAN_ARGS) : launch_decay_scan<NR, G, false>(JLX_SCAN_ARGS)
+#define JLX_SCAN_G(NR)                        \
+  {                                           \
+    const int g = scan_row_groups(H, dv, NR); \
+    if (g == 4) { JLX_SCAN(NR, 4); }          \
+    if (g == 2) { JLX_SCAN(NR, 2); }          \
+    JLX_SCAN(NR, 1);                          \
+  }
+  if (dk <= 32) {
+    if (scan_row_groups(H, dv, 8) >= 2) { JLX_SCAN(8, 2); }
+    JLX_SCAN(8, 1);
+  }
+  if (dk <= 128) JLX_SCAN_G(16)
+  if (dk <= 256) JLX_SCAN_G(32)
+  JLX_SCAN_G(64)
+#undef JLX_SCAN_G
 #undef JLX_SCAN
+#undef JLX_SCAN_ARGS
 }
 
 // ------------------------------------------------------------------------------------------------ head norm + gate

@@ -3,6 +3,7 @@
     python -m jax_llm_examples_b200.kernels.microbench attention_decode --batch 8 --context 8192
     python -m jax_llm_examples_b200.kernels.microbench attention_prefill --tokens 2048
     python -m jax_llm_examples_b200.kernels.microbench gemm --rows 8 --n 16384 --k 5120 [--experts 16] [--swiglu]
+    python -m jax_llm_examples_b200.kernels.microbench decay_scan --tokens 2048 --requests 1 --heads 16 [--read-before]
 
 The reference benchmarks its kernels the same way, from ``__main__`` blocks in the kernel files
 (llama4/llama4_jax/ragged_attention.py:299-418, llama4/llama4_jax/decode_ragged_dot.py:239-291).
@@ -130,6 +131,28 @@ def gemm(a) -> dict:
             "TFLOP/s": round(flops / t / 1e12, 1)}
 
 
+def decay_scan(a) -> dict:
+    """The decayed linear-attention recurrence: ``requests`` requests of ``tokens`` tokens each in one launch."""
+    dev = "cuda"
+    N, H, dk, dv = a.requests * a.tokens, a.heads, a.dim, a.vdim
+    q, k = torch.randn(N, H, dk, device=dev), torch.randn(N, H, dk, device=dev) * dk ** -0.5
+    d, v = torch.rand(N, H, dk, device=dev) * 0.5 + 0.5, torch.randn(N, H, dv, device=dev)
+    bonus = torch.randn(H, dk, device=dev) if a.read_before else None
+    state, o = torch.zeros(a.requests, H, dk, dv, device=dev), torch.empty(N, H, dv, device=dev)
+    cu = (torch.arange(a.requests + 1, device=dev, dtype=torch.int32) * a.tokens).contiguous()
+    slots = torch.arange(a.requests, device=dev, dtype=torch.int32)
+
+    def run():
+        K.decay_scan(q, k, d, v, bonus, state, cu, slots, o, not a.read_before)
+
+    t = _time(run, a.reps, _flush(a))
+    rows, states = N * H * (3 * dk + 2 * dv) * 4, a.requests * H * dk * dv * 8
+    return {"kernel": "decay_scan", "requests": a.requests, "tokens": a.tokens, "heads": H, "dim": dk, "vdim": dv,
+            "read": "before the update, with a bonus" if a.read_before else "after the update", "us": round(t * 1e6, 1),
+            "ns_per_token": round(t * 1e9 / a.tokens, 1), "bytes": rows + states, "GB/s": round((rows + states) / t / 1e9, 1),
+            "GFLOP/s": round(N * H * dk * dv * 5 / t / 1e9, 1)}
+
+
 def _flush(a):
     return None if a.no_flush else torch.empty(256 * 1024 * 1024 // 4, device="cuda")
 
@@ -137,10 +160,17 @@ def _flush(a):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "attention_prefill", "gemm"):
+    for name in ("attention_decode", "attention_prefill", "gemm", "decay_scan"):
         p = sub.add_parser(name)
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
+        if name == "decay_scan":
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--requests", type=int, default=1)
+            p.add_argument("--heads", type=int, default=16)
+            p.add_argument("--dim", type=int, default=128)
+            p.add_argument("--vdim", type=int, default=128)
+            p.add_argument("--read-before", action="store_true", help="o from the state before the update, with a bonus (time mixing)")
         if name.startswith("attention"):
             p.add_argument("--heads", type=int, default=40)
             p.add_argument("--kv-heads", type=int, default=8)
@@ -163,7 +193,7 @@ def main(argv=None) -> int:
             p.add_argument("--hint", type=int, default=0, help="rows per group that the token tile is sized for (0: twice the mean)")
             p.add_argument("--swiglu", action="store_true", help="fused SiLU(gate) * up epilogue")
     a = ap.parse_args(argv)
-    print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm}[a.what](a)))
+    print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "decay_scan": decay_scan}[a.what](a)))
     return 0
 
 
