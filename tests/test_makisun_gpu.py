@@ -334,6 +334,45 @@ def test_windowed_gated_attention_part_over_scattered_pages(name, dtype, tol, m)
 
 
 @pytest.mark.parametrize("name, dtype, tol", DTYPES)
+def test_two_mixers_side_by_side_share_their_products(name, dtype, tol):
+    """left_scale * attention + right_scale * linear attention through ONE input product and ONE output product, against
+    the plain sum of the two plain mixers: a portion of more than 256 rows (the mixers run one after the other), a short
+    portion and single tokens (the second mixer runs on another stream), states and pages carried between them."""
+    from jax_llm_examples_b200.parts import GatedLinearAttention, LayerCache, ParallelMixers, Runtime
+
+    torch.manual_seed(9)
+    D, eps, T = 40, 1e-5, 300
+    rt = Runtime(dtype, torch.device(DEV))
+    g = lambda *s: torch.randn(*s) * 0.3
+    m = {"left": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "mask": {"size": 37}, "rot": {"base": 1000.0, "dims": 6}, "scale": 0.3},
+         "right": {"heads": 3, "dim": 8, "vdim": 5, "tau": 4.0}, "left_scale": 1.3, "right_scale": 0.6}
+    a, r = m["left"], m["right"]
+    w = {"left.q": g(32, D), "left.k": g(16, D), "left.v": g(24, D), "left.g": g(4, D), "left.q.norm": 1 + 0.2 * torch.randn(8),
+         "left.k.norm": 1 + 0.2 * torch.randn(8), "left.o": g(D, 48),
+         "right.q": g(24, D), "right.k": g(24, D), "right.v": g(15, D), "right.g": g(15, D), "right.a1": g(4, D), "right.a2": g(24, 4),
+         "right.a2.b": g(24) + 2.0, "right.norm": 1 + 0.2 * torch.randn(5), "right.o": g(D, 15)}
+    wd = {k: v.to(dtype) for k, v in w.items()}
+    d = lambda k: wd[k].to(DEV)
+    left = _attention_part({k[5:]: v for k, v in wd.items() if k.startswith("left.")}, a, eps, dtype)
+    right = GatedLinearAttention(torch.cat([d("right.q"), d("right.k"), d("right.v"), d("right.g")]), d("right.a1"), d("right.a2"),
+                                 d("right.a2.b"), d("right.norm"), d("right.o"), 3, 8, 5, 4.0, eps)
+    both = ParallelMixers([left, right], [1.3, 0.6])
+    assert both.kv_need() == left.kv_need() and len(both.state_needs()) == 1 and both.w_in.shape[0] == 76 + 78 and both.w_o.shape == (D, 63)
+    pages = torch.zeros(40, 2, 2, 16, both.kv_need().head_dim, device=DEV, dtype=dtype)
+    table = torch.randperm(40)[:19].reshape(1, 19).to(torch.int32).to(DEV)
+    state = torch.zeros(2, 3, 8, 5, device=DEV)
+    hs = torch.randn(T, D).to(dtype)
+    outs = []
+    for lo, hi in ((0, 270), (270, 298), (298, 299), (299, 300)):
+        ctx = _ctx(rt, [hi - lo], [lo], [1], planners=both.step_planners() or left.step_planners())
+        outs.append(H.as_rows_sum(both.forward(ctx, hs[lo:hi].to(DEV), LayerCache(pages, table, True, state, (state,)))))
+        assert int(ctx.status) == 0
+    ref = plain.parallel_mixer(hs.double(), {"m." + k: v.double() for k, v in wd.items()}, "m.", m, eps)
+    _close(torch.cat(outs), ref, tol, name)
+    assert float(state[0].abs().max()) == 0.0 and float(state[1].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("name, dtype, tol", DTYPES)
 @pytest.mark.parametrize("window", [5, 16, 21, 64])
 def test_a_key_just_inside_and_just_outside_the_window(name, dtype, tol, window):
     """Made so that a fault shows: queries and keys are the (normed) hidden state itself, and ONE earlier token points
