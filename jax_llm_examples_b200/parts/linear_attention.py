@@ -93,6 +93,7 @@ class TimeMixWKV(Mixer):
     kernel_libraries = ("decay_scan", "gemm_simt", "group_norm")
     kernel_libraries_bf16 = ("gemm_stream",)
     needs_f32_input = True
+    OVERLAP_MAX_ROWS = 256
 
     def __init__(self, mu: torch.Tensor, w_rkvg: torch.Tensor, w_w1: torch.Tensor, w_w2: torch.Tensor, w0: torch.Tensor,
                  bonus: torch.Tensor, norm_weight: torch.Tensor, w_o: torch.Tensor, heads: int, dim: int, eps: float):
@@ -117,14 +118,29 @@ class TimeMixWKV(Mixer):
         blends = torch.empty((5, n, D), dtype=dt, device=h32.device)
         offsets = torch.empty(6, dtype=torch.int32, device=h32.device)  # row offsets of the blends: the groups of the product below
         K.token_shift_blend(h32, self.mu, shift_state, ctx.cu_q, ctx.slot_ids, ctx.req_of_token, blends, offsets)
-        with scope("qkv_matmul"):
-            # the four projections, each of its own blend, as one grouped product over the stacked rows
-            rkvg = as_rows(grouped_linear(ctx, blends[:4].view(4 * n, D), self.w_rkvg, offsets,
-                                          torch.float32, partials=True, largest_group=n))
+        def decay_logits():
             w1 = as_rows(linear(ctx, blends[4], self.w_w1, torch.float32, partials=True))
             lora = torch.empty((n, self.w_w1.shape[0]), dtype=dt, device=h32.device)
             K.bias_act(w1.data, lora, None, None, "tanh", w1.splits)
-            z = as_rows(linear(ctx, lora, self.w_w2, torch.float32, partials=True))
+            return as_rows(linear(ctx, lora, self.w_w2, torch.float32, partials=True))
+
+        with scope("qkv_matmul"):
+            # In steps of few rows the decay's three small launches run on the second stream beside the projections
+            # (a branch of a captured graph): the chain of dependent launches is shorter by them.
+            side = None
+            if ctx.workspace is not None and h32.is_cuda and n <= self.OVERLAP_MAX_ROWS:
+                main, side = torch.cuda.current_stream(), ctx.workspace.side_stream()
+                side.wait_stream(main)  # the blends are there
+                with torch.cuda.stream(side):
+                    z = decay_logits()
+                z.data.record_stream(main)  # made on the second stream, read (and freed) on the step's own
+            # the four projections, each of its own blend, as one grouped product over the stacked rows
+            rkvg = as_rows(grouped_linear(ctx, blends[:4].view(4 * n, D), self.w_rkvg, offsets,
+                                          torch.float32, partials=True, largest_group=n))
+            if side is None:
+                z = decay_logits()
+            else:
+                torch.cuda.current_stream().wait_stream(side)
         view = lambda i: K.rows_view(rkvg.data, rkvg.splits, 0, i * n)  # noqa: E731
         out = torch.empty((n, F), dtype=dt, device=h32.device)
         with scope("attention"):
