@@ -373,8 +373,9 @@ def test_two_mixers_side_by_side_share_their_products(name, dtype, tol):
 
 
 @pytest.mark.parametrize("name, dtype, tol", DTYPES)
+@pytest.mark.parametrize("size", [16, 128])  # padded to 64 in bfloat16 (the mma.sync kernels), and the tcgen05 kernel's size
 @pytest.mark.parametrize("window", [5, 16, 21, 64])
-def test_a_key_just_inside_and_just_outside_the_window(name, dtype, tol, window):
+def test_a_key_just_inside_and_just_outside_the_window(name, dtype, tol, window, size):
     """Made so that a fault shows: queries and keys are the (normed) hidden state itself, and ONE earlier token points
     where the query points, with a score that outweighs everything; its value is a marker.  Placed window - 1 tokens
     back it must be all the query sees; placed window tokens back it must be gone.  In a prompt portion and for a
@@ -382,8 +383,7 @@ def test_a_key_just_inside_and_just_outside_the_window(name, dtype, tol, window)
     from jax_llm_examples_b200.parts import GatedPagedAttention, LayerCache, Runtime
 
     torch.manual_seed(window)
-    D = dk = 16
-    dv = 16
+    D = dk = dv = size
     rt = Runtime(dtype, torch.device(DEV))
     eye = torch.eye(D)
     w_in = torch.cat([eye, eye, eye, torch.zeros(1, D)]).to(dtype).to(DEV)  # q = k = v = h; gate logit 0: a half
@@ -398,16 +398,19 @@ def test_a_key_just_inside_and_just_outside_the_window(name, dtype, tol, window)
             direction = torch.zeros(D)
             direction[3] = 4.0
             hs[qpos] = direction
-            hs[qpos - back] = direction + torch.tensor([0.0] * 8 + [1.0] + [0.0] * 7)  # the marker: entry 8
+            hs[qpos - back] = direction + torch.nn.functional.one_hot(torch.tensor(8), D).float()  # the marker: entry 8
             hs = hs.to(dtype)
-            pages = torch.zeros(12, 2, 1, 16, mixer.head_dim, device=DEV, dtype=dtype)
+            page = 64 if size == 128 else 16  # pages of 64: long portions of head size 128 go to the tcgen05 kernel
+            pages = torch.zeros(12, 2, 1, page, mixer.head_dim, device=DEV, dtype=dtype)
             table = torch.randperm(12)[:7].reshape(1, 7).to(torch.int32).to(DEV)
             cuts = [(0, qpos), (qpos, qpos + 1)] if decoded else [(0, qpos + 1)]
             out = None
             for lo, hi in cuts:
                 if hi > lo:
-                    ctx = _ctx(rt, [hi - lo], [lo], planners=mixer.step_planners())
+                    ctx = _ctx(rt, [hi - lo], [lo], planners=mixer.step_planners(), page_size=page)
                     out = H.as_rows_sum(mixer.forward(ctx, hs[lo:hi].to(DEV), LayerCache(pages, table, True, None)))
+            if size == 128 and dtype == torch.bfloat16 and not decoded and qpos >= 63:
+                assert any("tc" in kinds for kinds in ctx.scratch.get("attention_kernels", ())), "the tcgen05 kernel did not run"
             marker = 2.0 * float(out[-1, 8])  # the gate halves
             # seen: the needle shares the weight with the query itself (equal scores up to the marker's part): about a half
             assert (marker > 0.4) == seen and (seen or abs(marker) < 0.05), \
